@@ -1,0 +1,239 @@
+"""ctypes bindings for the CPU checkers -- TEST INFRASTRUCTURE.
+
+Two libraries expose the same head-level interface under different prefixes:
+
+* ``liboracle.so``  (prefix ``orc_``): the plain-C restatement in
+  ``adaptq_oracle.c``; always buildable (``make -C oracle``).
+* ``_ref/libadaptq_ref.so`` (prefix ``ref_``): the upstream C++ sources
+  compiled by ``build_ref.sh``; present only where that script could run (or
+  where its output was carried along).
+
+Only tests, the smoke check and the CPU-baseline leg of the benchmark import
+this module.  The product package never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_f32p = C.POINTER(C.c_float)
+_u8p = C.POINTER(C.c_uint8)
+_i8p = C.POINTER(C.c_int8)
+
+
+def _ptr(a, t):
+    return a.ctypes.data_as(t)
+
+
+def build_oracle() -> str:
+    """Compile liboracle.so if missing or stale; return its path."""
+    so = os.path.join(_HERE, "liboracle.so")
+    src = os.path.join(_HERE, "adaptq_oracle.c")
+    if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(
+            ["gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-w", "-o", so, src, "-lm"])
+    return so
+
+
+def ref_path(fast: bool = False) -> str:
+    return os.path.join(_HERE, "_ref", "libadaptq_ref_fast.so" if fast else "libadaptq_ref.so")
+
+
+def ref_available(fast: bool = False) -> bool:
+    return os.path.exists(ref_path(fast))
+
+
+class _Lib:
+    """Head-level interface shared by both libraries."""
+
+    def __init__(self, path: str, prefix: str):
+        self.lib = C.CDLL(path)
+        self.prefix = prefix
+        L = self.lib
+        g = lambda name: getattr(L, prefix + name)
+        self.head_create = g("head_create")
+        self.head_create.restype = C.c_void_p
+        self.head_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_float, C.c_int]
+        self.head_destroy = g("head_destroy"); self.head_destroy.argtypes = [C.c_void_p]; self.head_destroy.restype = None
+        self.head_append = g("head_append"); self.head_append.argtypes = [C.c_void_p, _f32p, _f32p, C.c_int]; self.head_append.restype = None
+        self.head_append_many = g("head_append_many"); self.head_append_many.argtypes = [C.c_void_p, _f32p, _f32p, C.c_int, C.c_int]; self.head_append_many.restype = None
+        self.head_compute = g("head_compute"); self.head_compute.argtypes = [C.c_void_p, _f32p, _f32p]; self.head_compute.restype = C.c_int
+        self.head_compute_batch = g("head_compute_batch"); self.head_compute_batch.argtypes = [C.c_void_p, _f32p, C.c_int, _f32p]; self.head_compute_batch.restype = C.c_int
+        self.head_reset = g("head_reset"); self.head_reset.argtypes = [C.c_void_p]; self.head_reset.restype = None
+        for name, rt in [("head_k_data", _u8p), ("head_v_data", _u8p), ("head_k_scale", _f32p),
+                         ("head_v_scale", _f32p), ("head_signs", _i8p)]:
+            f = g(name); f.argtypes = [C.c_void_p]; f.restype = rt; setattr(self, name, f)
+        for name in ["head_ring_head", "head_size", "head_padded", "head_k_row_bytes",
+                     "head_v_row_bytes", "head_mirror_tokens"]:
+            f = g(name); f.argtypes = [C.c_void_p]; f.restype = C.c_int; setattr(self, name, f)
+        self.head_kv_bytes = g("head_kv_bytes"); self.head_kv_bytes.argtypes = [C.c_void_p]; self.head_kv_bytes.restype = C.c_size_t
+        self.next_pow2 = g("next_pow2"); self.next_pow2.argtypes = [C.c_int]; self.next_pow2.restype = C.c_int
+        self.gen_rademacher = g("gen_rademacher"); self.gen_rademacher.argtypes = [_i8p, C.c_int, C.c_uint64]; self.gen_rademacher.restype = None
+        self.fwht_forward = g("fwht_forward"); self.fwht_forward.argtypes = [_f32p, _i8p, C.c_int]
+        self.fwht_inverse = g("fwht_inverse"); self.fwht_inverse.argtypes = [_f32p, _i8p, C.c_int]
+        self.quantize_fast = g("quantize_fast"); self.quantize_fast.argtypes = [C.c_float, C.c_int]; self.quantize_fast.restype = C.c_int
+        self.pack_indices = g("pack_indices"); self.pack_indices.argtypes = [_u8p, C.c_int, C.c_int, _u8p]; self.pack_indices.restype = C.c_int
+        self.unpack_indices = g("unpack_indices"); self.unpack_indices.argtypes = [_u8p, C.c_int, C.c_int, _u8p]; self.unpack_indices.restype = C.c_int
+        self.codebook = g("codebook"); self.codebook.argtypes = [C.c_int]; self.codebook.restype = _f32p
+        self.codebook_size = g("codebook_size"); self.codebook_size.argtypes = [C.c_int]; self.codebook_size.restype = C.c_int
+
+    # -- numpy conveniences -------------------------------------------------
+    def signs(self, n: int, seed: int) -> np.ndarray:
+        d = np.zeros(n, dtype=np.int8)
+        self.gen_rademacher(_ptr(d, _i8p), n, C.c_uint64(seed & (2**64 - 1)))
+        return d
+
+    def fwht(self, x: np.ndarray, signs: np.ndarray, inverse: bool = False) -> np.ndarray:
+        y = np.ascontiguousarray(x, dtype=np.float32).copy()
+        s = np.ascontiguousarray(signs, dtype=np.int8)
+        (self.fwht_inverse if inverse else self.fwht_forward)(_ptr(y, _f32p), _ptr(s, _i8p), len(y))
+        return y
+
+    def pack(self, idx: np.ndarray, bits: int) -> np.ndarray:
+        idx = np.ascontiguousarray(idx, dtype=np.uint8)
+        out = np.zeros((len(idx) * bits + 7) // 8, dtype=np.uint8)
+        rc = self.pack_indices(_ptr(idx, _u8p), len(idx), bits, _ptr(out, _u8p))
+        if rc != 0:
+            raise ValueError("unsupported bit width")
+        return out
+
+    def unpack(self, packed: np.ndarray, d: int, bits: int) -> np.ndarray:
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        out = np.zeros(d, dtype=np.uint8)
+        rc = self.unpack_indices(_ptr(packed, _u8p), d, bits, _ptr(out, _u8p))
+        if rc != 0:
+            raise ValueError("unsupported bit width")
+        return out
+
+    def centroids(self, bits: int) -> np.ndarray:
+        n = self.codebook_size(bits)
+        p = self.codebook(bits)
+        return np.array([p[i] for i in range(n)], dtype=np.float32)
+
+
+class Head:
+    """One attention head on the CPU checker `lib` (an `_Lib`)."""
+
+    def __init__(self, lib: _Lib, dim, k_bits, v_bits, capacity, seed, v_mass=0.0, hybrid_thresh=0):
+        self.L = lib
+        self.dim = dim
+        self.h = lib.head_create(dim, k_bits, v_bits, capacity, C.c_uint64(seed & (2**64 - 1)),
+                                 C.c_float(v_mass), hybrid_thresh)
+        if not self.h:
+            raise ValueError("head_create rejected the arguments")
+        self.capacity = capacity
+
+    def close(self):
+        if self.h:
+            self.L.head_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def append(self, k, v, pos=0):
+        k = np.ascontiguousarray(k, dtype=np.float32); v = np.ascontiguousarray(v, dtype=np.float32)
+        self.L.head_append(self.h, _ptr(k, _f32p), _ptr(v, _f32p), pos)
+
+    def append_many(self, keys, vals, pos0=0):
+        keys = np.ascontiguousarray(keys, dtype=np.float32); vals = np.ascontiguousarray(vals, dtype=np.float32)
+        assert keys.shape == vals.shape and keys.shape[1] == self.dim
+        self.L.head_append_many(self.h, _ptr(keys, _f32p), _ptr(vals, _f32p), keys.shape[0], pos0)
+
+    def compute(self, q):
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        out = np.zeros(self.dim, dtype=np.float32)
+        n = self.L.head_compute(self.h, _ptr(q, _f32p), _ptr(out, _f32p))
+        return out, n
+
+    def compute_batch(self, qs):
+        qs = np.ascontiguousarray(qs, dtype=np.float32)
+        out = np.zeros_like(qs)
+        n = self.L.head_compute_batch(self.h, _ptr(qs, _f32p), qs.shape[0], _ptr(out, _f32p))
+        return out, n
+
+    def reset(self):
+        self.L.head_reset(self.h)
+
+    @property
+    def size(self): return self.L.head_size(self.h)
+    @property
+    def ring_head(self): return self.L.head_ring_head(self.h)
+    @property
+    def padded(self): return self.L.head_padded(self.h)
+    @property
+    def k_row_bytes(self): return self.L.head_k_row_bytes(self.h)
+    @property
+    def v_row_bytes(self): return self.L.head_v_row_bytes(self.h)
+    @property
+    def mirror_tokens(self): return self.L.head_mirror_tokens(self.h)
+    @property
+    def kv_bytes(self): return self.L.head_kv_bytes(self.h)
+
+    def _arr(self, p, n, dt):
+        if n == 0:
+            return np.zeros(0, dtype=dt)
+        return np.ctypeslib.as_array(p, shape=(n,)).astype(dt, copy=True)
+
+    def k_data(self): return self._arr(self.L.head_k_data(self.h), self.capacity * self.k_row_bytes, np.uint8).reshape(self.capacity, -1)
+    def v_data(self): return self._arr(self.L.head_v_data(self.h), self.capacity * self.v_row_bytes, np.uint8).reshape(self.capacity, -1)
+    def k_scale(self): return self._arr(self.L.head_k_scale(self.h), self.capacity, np.float32)
+    def v_scale(self): return self._arr(self.L.head_v_scale(self.h), self.capacity, np.float32)
+    def signs(self): return self._arr(self.L.head_signs(self.h), self.padded, np.int8)
+
+
+_cache = {}
+
+
+def oracle() -> _Lib:
+    if "orc" not in _cache:
+        _cache["orc"] = _Lib(build_oracle(), "orc_")
+    return _cache["orc"]
+
+
+def reference(fast: bool = False) -> _Lib:
+    key = "ref_fast" if fast else "ref"
+    if key not in _cache:
+        if not ref_available(fast):
+            raise FileNotFoundError(ref_path(fast) + " (run oracle/build_ref.sh where the upstream sources are)")
+        _cache[key] = _Lib(ref_path(fast), "ref_")
+    return _cache[key]
+
+
+def mha_head_seed(base_seed: int, head_idx: int) -> int:
+    """Per-head seed rule of the multi-head handle (upstream core/adaptq_c_api.cpp:160)."""
+    return (base_seed ^ (head_idx * 0xDEADBEEFCAFE)) & (2**64 - 1)
+
+
+def time_reference_heads(n_heads, dim, k_bits, v_bits, capacity, base_seed, keys, vals, queries,
+                         n_steps, n_threads, v_mass=0.0, hybrid_thresh=0, fast=True):
+    """Run the upstream build's timing harness. keys/vals: [n_heads, n_tokens, dim]."""
+    L = reference(fast).lib
+    f = L.ref_time_heads
+    f.restype = C.c_int
+    f.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_float, C.c_int,
+                  _f32p, _f32p, C.c_int, _f32p, C.c_int, _f32p, C.c_int,
+                  C.POINTER(C.c_double), C.POINTER(C.c_double)]
+    keys = np.ascontiguousarray(keys, dtype=np.float32); vals = np.ascontiguousarray(vals, dtype=np.float32)
+    queries = np.ascontiguousarray(queries, dtype=np.float32)
+    outs = np.zeros((n_heads, dim), dtype=np.float32)
+    ta, tc = C.c_double(0), C.c_double(0)
+    rc = f(n_heads, dim, k_bits, v_bits, capacity, C.c_uint64(base_seed), C.c_float(v_mass), hybrid_thresh,
+           _ptr(keys, _f32p), _ptr(vals, _f32p), keys.shape[1], _ptr(queries, _f32p), n_steps,
+           _ptr(outs, _f32p), n_threads, C.byref(ta), C.byref(tc))
+    if rc != 0:
+        raise RuntimeError("ref_time_heads failed")
+    return ta.value, tc.value, outs
+
+
+def ref_max_threads() -> int:
+    L = reference(True).lib
+    L.ref_max_threads.restype = C.c_int
+    return L.ref_max_threads()

@@ -1,0 +1,20 @@
+"""adaptq_b200 -- the AdapTQ quantized KV-cache append / decode-attention path on
+NVIDIA B200 (sm_100a), behind upstream's own interfaces:
+
+* the C ABI of include/adaptq.h (+ batched additions in include/adaptq_b200.h),
+  implemented by ``libadaptq_b200.so``;
+* ``MHAContext`` (upstream's pybind class ``adaptq_py.MHAContext``);
+* ``Engine`` (upstream ``adaptq.Engine``) and ``AdaptQAttention``.
+"""
+from ._lib import LIB_PATH, last_error, load  # noqa: F401
+from .core import Engine  # noqa: F401
+from .mha import MHAContext  # noqa: F401
+
+__version__ = "0.1.0"
+
+
+def __getattr__(name):
+    if name == "AdaptQAttention":  # lazy: importing torch is slow
+        from .torch_adapter import AdaptQAttention
+        return AdaptQAttention
+    raise AttributeError(name)

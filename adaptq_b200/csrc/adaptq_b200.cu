@@ -1,0 +1,1001 @@
+// Host runtime and C ABI of the B200 AdapTQ engine (libadaptq_b200.so).
+//
+// Implements include/adaptq.h (the interface of upstream
+// core/adaptq_c_api.cpp) and include/adaptq_b200.h over the CUDA kernels in
+// this directory.  There is no CPU compute path: if no CUDA device is usable
+// every constructor fails with an error string.
+#include "../../include/adaptq_b200.h"
+#include "append.cuh"
+#include "compute_general.cuh"
+#include "compute_stream.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <cub/device/device_segmented_radix_sort.cuh>
+#include <mutex>
+#include <new>
+#include <vector>
+
+using namespace aq;
+
+// ---------------------------------------------------------------------------
+// error string (per thread, 256 bytes, as upstream core/adaptq_c_api.cpp:15-21)
+// ---------------------------------------------------------------------------
+static thread_local char tl_error[256] = "";
+static void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+}
+static void clear_error() { tl_error[0] = '\0'; }
+extern "C" const char *adaptq_last_error(void) { return tl_error; }
+
+static std::atomic<unsigned long long> g_launches{0};
+static std::atomic<int> g_policy{0};
+extern "C" unsigned long long adaptq_kernel_launches(void) { return g_launches.load(); }
+extern "C" int adaptq_set_kernel_policy(int policy) {
+  if (policy < 0 || policy > 2) { set_error("adaptq_set_kernel_policy: policy must be 0, 1 or 2"); return -1; }
+  g_policy.store(policy);
+  return 0;
+}
+
+#define CUDA_TRY(expr, what)                                                            \
+  do {                                                                                  \
+    cudaError_t e__ = (expr);                                                           \
+    if (e__ != cudaSuccess) {                                                           \
+      set_error("%s: CUDA error: %s", what, cudaGetErrorString(e__));                   \
+      return false;                                                                     \
+    }                                                                                   \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// handle
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr uint32_t MAGIC = 0xA0DA97B2u;
+
+struct RingState { int head, size, mirror; };
+
+struct Group {
+  uint32_t magic = MAGIC;
+  bool single = false;
+  CacheView c{};
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  std::vector<uint64_t> seeds;
+  // ring state: one value while all heads move together, else one per head
+  bool uniform = true;
+  RingState u{0, 0, 0};
+  std::vector<RingState> per_head;
+  // device staging for host-pointer calls, and scratch for partials / sparse V
+  void *d_stage = nullptr; size_t stage_bytes = 0;
+  void *h_stage = nullptr; size_t h_stage_bytes = 0;
+  void *d_scratch = nullptr; size_t scratch_bytes = 0;
+  int *d_status = nullptr;
+  size_t device_bytes = 0;
+  std::mutex mu;
+
+  RingState state(int h) const { return uniform ? u : per_head[h]; }
+  void split_state() {
+    if (uniform) { per_head.assign(c.n_heads, u); uniform = false; }
+  }
+  void try_unify() {
+    if (uniform) return;
+    for (int i = 1; i < c.n_heads; ++i)
+      if (per_head[i].head != per_head[0].head || per_head[i].size != per_head[0].size ||
+          per_head[i].mirror != per_head[0].mirror)
+        return;
+    u = per_head[0]; uniform = true; per_head.clear();
+  }
+};
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
+  ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+int next_pow2(int n) { // upstream core/fwht.cpp:13-19
+  if (n <= 1) return 1;
+  if (n > (1 << 30)) return 1 << 30;
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+
+bool valid_bits(int b) { return b == 16 || (b >= 2 && b <= 4); }
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+__global__ void fill_f32_kernel(float *p, size_t n, float v) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
+}
+__global__ void segment_offsets_kernel(int *begin, int *end, int n_seg, int stride, int n) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_seg) { begin[i] = i * stride; end[i] = i * stride + n; }
+}
+
+void free_group(Group *g) {
+  if (!g) return;
+  DeviceGuard dg(g->device);
+  if (g->stream == nullptr || true) cudaDeviceSynchronize();
+  cudaFree(g->c.k_slab); cudaFree(g->c.v_slab); cudaFree(g->c.k_scale); cudaFree(g->c.v_scale);
+  cudaFree((void *)g->c.signs); cudaFree(g->c.mirror);
+  cudaFree(g->d_stage); cudaFree(g->d_scratch); cudaFree(g->d_status);
+  if (g->h_stage) cudaFreeHost(g->h_stage);
+  g->magic = 0;
+  delete g;
+}
+
+bool alloc(void **p, size_t bytes, Group *g, const char *what) {
+  *p = nullptr;
+  if (bytes == 0) bytes = 16;
+  cudaError_t e = cudaMalloc(p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error("%s: device allocation of %zu bytes failed: %s", what, bytes, cudaGetErrorString(e));
+    return false;
+  }
+  g->device_bytes += bytes;
+  return true;
+}
+
+// Rademacher signs as upstream core/fwht.cpp:21-27, stored one bit per sign.
+void sign_words_for(uint64_t seed, int padded, uint32_t *words, int n_words) {
+  uint64_t s = seed ? seed : 0xdeadbeefcafe1234ULL;
+  for (int i = 0; i < n_words; ++i) words[i] = 0;
+  for (int i = 0; i < padded; ++i) {
+    s ^= s << 13; s ^= s >> 7; s ^= s << 17;
+    if (!(s & 1)) words[i >> 5] |= 1u << (i & 31);
+  }
+}
+
+Group *create_group(const char *fn, const char *bad_args_msg, int n_heads, const uint64_t *seeds, int dim,
+                    int k_bits, int v_bits, int capacity, float v_mass, int hyb, bool single) {
+  if (n_heads <= 0 || dim <= 0 || !valid_bits(k_bits) || !valid_bits(v_bits) || capacity < 0 || hyb < 0) {
+    set_error("%s", bad_args_msg);
+    return nullptr;
+  }
+  const int P = next_pow2(dim);
+  if (P > 1024) { // upstream throws here (core/quantizer.cpp:27-31); the C ABI must not
+    set_error("%s: head dimension %d pads to %d, above the supported 1024", fn, dim, P);
+    return nullptr;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    set_error("%s: no usable CUDA device (this library has no CPU path)", fn);
+    return nullptr;
+  }
+  Group *g = new (std::nothrow) Group();
+  if (!g) { set_error("%s: out of host memory", fn); return nullptr; }
+  g->single = single;
+  g->device = dev;
+  cudaDeviceGetAttribute(&g->sm_count, cudaDevAttrMultiProcessorCount, dev);
+  g->seeds.assign(seeds, seeds + n_heads);
+  CacheView &c = g->c;
+  c.n_heads = n_heads; c.dim = dim; c.padded = P; c.k_bits = k_bits; c.v_bits = v_bits;
+  c.log2p = 0; while ((1 << c.log2p) < P) ++c.log2p;
+  c.k_row = row_bytes(P, k_bits); c.v_row = row_bytes(P, v_bits);
+  c.cap = capacity; c.hyb = hyb; c.v_mass = v_mass;
+  // +128 slack: bulk copies of the last tile round their size up to 16 bytes
+  c.k_stride = round_up((size_t)capacity * c.k_row, 128) + 128;
+  c.v_stride = round_up((size_t)capacity * c.v_row, 128) + 128;
+  c.s_stride = (int)round_up((size_t)capacity, 32) + 32;
+  c.sign_words = (P + 31) / 32;
+  c.mirror_stride = (size_t)hyb * 2 * dim;
+  const char *what = fn;
+  bool ok = alloc((void **)&c.k_slab, c.k_stride * n_heads, g, what) &&
+            alloc((void **)&c.v_slab, c.v_stride * n_heads, g, what) &&
+            alloc((void **)&c.k_scale, (size_t)c.s_stride * n_heads * 4, g, what) &&
+            alloc((void **)&c.v_scale, (size_t)c.s_stride * n_heads * 4, g, what) &&
+            alloc((void **)&c.signs, (size_t)c.sign_words * n_heads * 4, g, what) &&
+            alloc((void **)&g->d_status, 16, g, what);
+  if (ok && hyb > 0) ok = alloc((void **)&c.mirror, c.mirror_stride * n_heads * 4, g, what);
+  if (!ok) { free_group(g); return nullptr; }
+  std::vector<uint32_t> words((size_t)c.sign_words * n_heads);
+  for (int h = 0; h < n_heads; ++h) sign_words_for(seeds[h], P, words.data() + (size_t)h * c.sign_words, c.sign_words);
+  cudaError_t e = cudaMemcpy((void *)c.signs, words.data(), words.size() * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemset(c.k_slab, 0, c.k_stride * n_heads);
+  if (e == cudaSuccess) e = cudaMemset(c.v_slab, 0, c.v_stride * n_heads);
+  if (e == cudaSuccess) e = cudaMemset(g->d_status, 0, 16);
+  if (e == cudaSuccess) {
+    size_t ns = (size_t)c.s_stride * n_heads;
+    fill_f32_kernel<<<(int)std::min<size_t>((ns + 255) / 256, 4096), 256>>>(c.k_scale, ns, 1.0f);
+    fill_f32_kernel<<<(int)std::min<size_t>((ns + 255) / 256, 4096), 256>>>(c.v_scale, ns, 1.0f);
+    g_launches += 2;
+    e = cudaDeviceSynchronize();
+  }
+  if (e != cudaSuccess) {
+    set_error("%s: CUDA error during set-up: %s", fn, cudaGetErrorString(e));
+    cudaGetLastError();
+    free_group(g);
+    return nullptr;
+  }
+  return g;
+}
+
+Group *as_group(void *h) {
+  Group *g = static_cast<Group *>(h);
+  return (g && g->magic == MAGIC) ? g : nullptr;
+}
+
+enum PtrKind { PK_HOST_PAGEABLE, PK_HOST_PINNED, PK_DEVICE };
+PtrKind ptr_kind(const void *p) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return PK_HOST_PAGEABLE; }
+  if (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) return PK_DEVICE;
+  if (at.type == cudaMemoryTypeHost) return PK_HOST_PINNED;
+  return PK_HOST_PAGEABLE;
+}
+
+bool ensure_stage(Group *g, size_t dev_bytes, size_t host_bytes) {
+  if (dev_bytes > g->stage_bytes) {
+    CUDA_TRY(cudaStreamSynchronize(g->stream), "staging");
+    if (g->d_stage) { cudaFree(g->d_stage); g->device_bytes -= g->stage_bytes; }
+    g->d_stage = nullptr; g->stage_bytes = 0;
+    size_t nb = round_up(dev_bytes, 256);
+    if (!alloc(&g->d_stage, nb, g, "staging")) return false;
+    g->stage_bytes = nb;
+  }
+  if (host_bytes > g->h_stage_bytes) {
+    CUDA_TRY(cudaStreamSynchronize(g->stream), "staging");
+    if (g->h_stage) cudaFreeHost(g->h_stage);
+    g->h_stage = nullptr; g->h_stage_bytes = 0;
+    size_t nb = round_up(host_bytes, 4096);
+    CUDA_TRY(cudaMallocHost(&g->h_stage, nb), "staging (pinned host)");
+    g->h_stage_bytes = nb;
+  }
+  return true;
+}
+
+bool ensure_scratch(Group *g, size_t bytes) {
+  if (bytes <= g->scratch_bytes) return true;
+  CUDA_TRY(cudaStreamSynchronize(g->stream), "scratch");
+  if (g->d_scratch) { cudaFree(g->d_scratch); g->device_bytes -= g->scratch_bytes; }
+  g->d_scratch = nullptr; g->scratch_bytes = 0;
+  size_t nb = round_up(bytes + bytes / 4, 256);
+  if (!alloc(&g->d_scratch, nb, g, "scratch")) return false;
+  g->scratch_bytes = nb;
+  return true;
+}
+
+// Bring `bytes` at `src` to the device: device pointers pass through, pinned
+// host memory is copied asynchronously, pageable memory goes through the
+// handle's pinned buffer.  `slot_off` places it inside the staging buffer.
+const float *to_device(Group *g, const void *src, size_t bytes, size_t slot_off, bool &ok) {
+  ok = true;
+  PtrKind k = ptr_kind(src);
+  if (k == PK_DEVICE) return static_cast<const float *>(src);
+  char *dst = static_cast<char *>(g->d_stage) + slot_off;
+  cudaError_t e;
+  if (k == PK_HOST_PINNED) {
+    e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g->stream);
+  } else {
+    char *hp = static_cast<char *>(g->h_stage) + slot_off;
+    memcpy(hp, src, bytes);
+    e = cudaMemcpyAsync(dst, hp, bytes, cudaMemcpyHostToDevice, g->stream);
+  }
+  if (e != cudaSuccess) { set_error("host-to-device copy failed: %s", cudaGetErrorString(e)); ok = false; }
+  return reinterpret_cast<const float *>(dst);
+}
+
+bool check_status(Group *g, const char *fn) {
+  int st[4] = {0, 0, 0, 0};
+  CUDA_TRY(cudaMemcpyAsync(st, g->d_status, sizeof(int), cudaMemcpyDeviceToHost, g->stream), fn);
+  CUDA_TRY(cudaStreamSynchronize(g->stream), fn);
+  if (st[0] != 0) {
+    set_error("%s: a kernel gave up waiting for a memory transfer (status %d)", fn, st[0]);
+    cudaMemsetAsync(g->d_status, 0, sizeof(int), g->stream);
+    return false;
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// append
+// ---------------------------------------------------------------------------
+template <int P, int BITS>
+bool launch_rows(Group *g, const AppendLaunch &a) {
+  constexpr int THREADS = 128;
+  constexpr size_t SMEM = (size_t)THREADS * (P + 4) * sizeof(float);
+  static bool configured[64] = {};
+  auto kern = append_rows_kernel<P, BITS, THREADS>;
+  if (!configured[g->device & 63]) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM), "append");
+    configured[g->device & 63] = true;
+  }
+  long long items = (long long)a.heads_in_call * a.n_tokens;
+  long long tiles = (items + THREADS - 1) / THREADS;
+  int per_sm = P == 128 ? 3 : 4;
+  int grid = (int)std::min<long long>(tiles, (long long)g->sm_count * per_sm);
+  kern<<<grid, THREADS, SMEM, g->stream>>>(a);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "append");
+  return true;
+}
+
+template <int P>
+bool launch_rows_bits(Group *g, const AppendLaunch &a, int bits) {
+  switch (bits) {
+  case 2: return launch_rows<P, 2>(g, a);
+  case 3: return launch_rows<P, 3>(g, a);
+  case 4: return launch_rows<P, 4>(g, a);
+  default: return launch_rows<P, 16>(g, a);
+  }
+}
+
+bool launch_append_one(Group *g, AppendLaunch a, int src_row_align_ok) {
+  const CacheView &c = g->c;
+  const int bits = a.which ? c.v_bits : c.k_bits;
+  const int policy = g_policy.load();
+  bool fast = policy != 1 && (c.padded == 64 || c.padded == 128) && (c.dim % 4 == 0) && src_row_align_ok;
+  if (fast) return c.padded == 128 ? launch_rows_bits<128>(g, a, bits) : launch_rows_bits<64>(g, a, bits);
+  if (policy == 2) { set_error("append: shape not covered by the specialised kernel"); return false; }
+  long long items = (long long)a.heads_in_call * a.n_tokens;
+  int grid = (int)std::min<long long>((items + GEN_WARPS - 1) / GEN_WARPS, (long long)g->sm_count * 16);
+  size_t smem = (size_t)GEN_WARPS * c.padded * sizeof(float);
+  append_general_kernel<<<grid, GEN_WARPS * 32, smem, g->stream>>>(a);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "append");
+  return true;
+}
+
+RingState advance(const CacheView &c, RingState s, int T) { // cache/ring_buffer.cpp:105-119, attention.cpp:354-365
+  RingState r = s;
+  if (c.cap > 0) {
+    r.head = (int)(((long long)s.head + T) % c.cap);
+    r.size = (int)std::min<long long>((long long)s.size + T, c.cap);
+  }
+  if (c.hyb > 0) {
+    bool evicts = (long long)s.size + T > c.cap;
+    if (evicts) r.mirror = 0;
+    else r.mirror = s.mirror + std::min(T, std::max(0, c.hyb - s.mirror));
+  }
+  return r;
+}
+
+// keys/vals on the device: [n_tokens] rows of `token_stride` floats, head hl at +hl*dim
+bool append_device(Group *g, const float *dk, const float *dv, int head0, int heads_in_call, int n_tokens,
+                   size_t token_stride, RingState st) {
+  if (n_tokens <= 0 || heads_in_call <= 0) return true;
+  AppendLaunch a;
+  a.c = g->c;
+  a.head0 = head0; a.heads_in_call = heads_in_call; a.n_tokens = n_tokens;
+  a.ring_head = st.head; a.ring_size = st.size; a.mirror_cnt = st.mirror;
+  a.head_major = n_tokens >= 32;
+  a.status = g->d_status;
+  a.src_token_stride = token_stride;
+  for (int which = 0; which < 2; ++which) {
+    a.which = which;
+    a.src = which ? dv : dk;
+    int align_ok = ((reinterpret_cast<uintptr_t>(a.src) & 15) == 0) && (token_stride % 4 == 0);
+    if (!launch_append_one(g, a, align_ok)) return false;
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// compute
+// ---------------------------------------------------------------------------
+size_t partial_floats(const CacheView &c) { return (size_t)2 + c.padded; }
+
+bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *partial_out) {
+  const CacheView &c = g->c;
+  const bool mirror = a.use_mirror != 0;
+  const bool k_f32 = mirror || c.k_bits == 16;
+  const bool v_f32 = mirror || c.v_bits == 16;
+  const int items = a.heads_in_call * a.nq;
+  int want = std::max(1, (2 * g->sm_count + items - 1) / items);
+  int max_splits = std::max(1, (a.n + 255) / 256);
+  a.n_splits = std::min(want, max_splits);
+  a.span = (int)round_up((size_t)(a.n + a.n_splits - 1) / a.n_splits, 32);
+  a.n_splits = (a.n + a.span - 1) / a.span;
+  a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
+  const int kcb = k_f32 ? 0 : (1 << c.k_bits);
+  size_t smem = cg_smem_floats(c.padded, kcb, a.chunk) * sizeof(float);
+  static int smem_set[64] = {};
+  if ((int)smem > smem_set[g->device & 63]) {
+    CUDA_TRY(cudaFuncSetAttribute(compute_general_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute");
+    smem_set[g->device & 63] = (int)smem;
+  }
+  const bool direct = a.n_splits == 1 && !want_partial_out;
+  if (!direct) {
+    if (!ensure_scratch(g, (size_t)a.n_splits * items * partial_floats(c) * sizeof(float))) return false;
+    a.partial = static_cast<float *>(g->d_scratch);
+    a.mode = 1;
+  } else {
+    a.mode = 0;
+  }
+  dim3 grid(a.n_splits, a.heads_in_call, a.nq);
+  compute_general_kernel<<<grid, CG_THREADS, smem, g->stream>>>(a);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "compute");
+  if (!direct) {
+    merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
+        a.partial, (size_t)items * partial_floats(c), a.n_splits, c, a.head0, a.nq,
+        want_partial_out ? partial_out : a.out, v_f32 ? 1 : 0, want_partial_out ? 1 : 0);
+    ++g_launches;
+    CUDA_TRY(cudaGetLastError(), "compute (merge)");
+  }
+  return true;
+}
+
+bool launch_sparse(Group *g, ComputeLaunch &a) {
+  const CacheView &c = g->c;
+  const int items = a.heads_in_call * a.nq;
+  const int ws = (int)round_up((size_t)a.n, 32);
+  const size_t cells = (size_t)items * ws;
+  size_t temp_bytes = 0;
+  cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
+                                                     (const int *)nullptr, (int *)nullptr, (int)cells, items,
+                                                     (const int *)nullptr, (const int *)nullptr, 0, 32, g->stream);
+  size_t off_w = 0, off_o = off_w + cells * 4, off_sw = off_o + cells * 4, off_so = off_sw + cells * 4;
+  size_t off_b = off_so + cells * 4, off_e = off_b + round_up((size_t)items * 4, 256);
+  size_t off_t = off_e + round_up((size_t)items * 4, 256);
+  if (!ensure_scratch(g, off_t + temp_bytes + 256)) return false;
+  char *base = static_cast<char *>(g->d_scratch);
+  float *w = (float *)(base + off_w), *sw = (float *)(base + off_sw);
+  int *o = (int *)(base + off_o), *so = (int *)(base + off_so);
+  int *sb = (int *)(base + off_b), *se = (int *)(base + off_e);
+  // 1. logits into the weight buffer (general kernel, mode 2)
+  a.weights = w; a.w_stride = ws; a.mode = 2;
+  a.n_splits = std::max(1, std::min((2 * g->sm_count + items - 1) / items, (a.n + 255) / 256));
+  a.span = (int)round_up((size_t)(a.n + a.n_splits - 1) / a.n_splits, 32);
+  a.n_splits = (a.n + a.span - 1) / a.span;
+  a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
+  size_t smem = cg_smem_floats(c.padded, 1 << c.k_bits, a.chunk) * sizeof(float);
+  static int smem_set[64] = {};
+  if ((int)smem > smem_set[g->device & 63]) {
+    CUDA_TRY(cudaFuncSetAttribute(compute_general_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute");
+    smem_set[g->device & 63] = (int)smem;
+  }
+  compute_general_kernel<<<dim3(a.n_splits, a.heads_in_call, a.nq), CG_THREADS, smem, g->stream>>>(a);
+  // 2. softmax weights, 3. stable descending sort per (head, query), 4. cut + accumulate
+  softmax_weights_kernel<<<items, CG_THREADS, 0, g->stream>>>(w, o, ws, a.n);
+  segment_offsets_kernel<<<(items + 255) / 256, 256, 0, g->stream>>>(sb, se, items, ws, a.n);
+  g_launches += 3;
+  cudaError_t e = cub::DeviceSegmentedRadixSort::SortPairsDescending(base + off_t, temp_bytes, w, sw, o, so, (int)cells,
+                                                                     items, sb, se, 0, 32, g->stream);
+  g_launches += 1;
+  CUDA_TRY(e, "compute (sparse-V sort)");
+  sparse_accumulate_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(sw, so, ws, a.n, c, a.head0, a.nq, a.out);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "compute (sparse V)");
+  return true;
+}
+
+
+// ---- streaming kernel dispatch ---------------------------------------------
+template <int KB, int KW, int VB, int VW>
+bool launch_stream_t(Group *g, const StreamLaunch &a, int grid) {
+  auto kern = compute_stream_kernel<KB, KW, VB, VW>;
+  static bool configured[64] = {};
+  if (!configured[g->device & 63]) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CS_SMEM_BYTES), "compute");
+    configured[g->device & 63] = true;
+  }
+  kern<<<grid, CS_THREADS, CS_SMEM_BYTES, g->stream>>>(a);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "compute");
+  return true;
+}
+
+bool stream_supported(const CacheView &c) {
+  if (c.padded == 128) return (c.k_bits == 4 || c.k_bits == 2) && (c.v_bits == 4 || c.v_bits == 2);
+  if (c.padded == 64) return c.k_bits == 4 && c.v_bits == 4;
+  return false;
+}
+
+// Pick the number of KV spans per (head, query): spans are multiples of 256
+// tokens, at most CS_SPAN_MAX, and the item count should fill whole waves of
+// persistent blocks.
+void plan_spans(int n, int items_base, int sms, int &n_splits, int &span) {
+  const int min_splits = (n + CS_SPAN_MAX - 1) / CS_SPAN_MAX;
+  int best_s = min_splits;
+  double best = -1.0;
+  for (int r = 1; r <= 16; ++r) {
+    int s = std::max(min_splits, (sms * r) / std::max(1, items_base));
+    s = std::max(1, s);
+    int sp = (int)round_up((size_t)(n + s - 1) / s, 256);
+    if (sp < 1024 && s > min_splits) {
+      sp = 1024;
+    }
+    sp = std::min(sp, CS_SPAN_MAX);
+    int s2 = (n + sp - 1) / sp;
+    long long items = (long long)items_base * s2;
+    long long waves = (items + sms - 1) / sms;
+    double fill = (double)items / (double)(waves * sms);
+    double overhead = (double)sp / (double)(sp + 700); // per-item table build / bucket fold
+    double score = fill * overhead;
+    if (score > best + 1e-9) { best = score; best_s = s2; span = sp; }
+  }
+  n_splits = best_s;
+  span = (int)std::min<size_t>(CS_SPAN_MAX, round_up((size_t)(n + n_splits - 1) / n_splits, 256));
+  n_splits = (n + span - 1) / span;
+}
+
+bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, float *partial_out) {
+  const CacheView &c = g->c;
+  StreamLaunch a{};
+  a.c = c; a.q = ca.q; a.out = ca.out; a.head0 = ca.head0; a.heads_in_call = ca.heads_in_call; a.nq = ca.nq;
+  a.n = ca.n; a.status = g->d_status;
+  const int items_base = a.heads_in_call * a.nq;
+  plan_spans(a.n, items_base, g->sm_count, a.n_splits, a.span);
+  const bool direct = a.n_splits == 1 && !want_partial_out;
+  if (!direct) {
+    if (a.n_splits == 1) {
+      a.partial = partial_out; // a single span already is the combined partial
+    } else {
+      if (!ensure_scratch(g, (size_t)a.n_splits * items_base * partial_floats(c) * sizeof(float))) return false;
+      a.partial = static_cast<float *>(g->d_scratch);
+    }
+  }
+  const int force_partial = (!direct && a.n_splits == 1) ? 1 : 0;
+  a.force_partial = force_partial;
+  const long long items = (long long)items_base * a.n_splits;
+  const int grid = (int)std::min<long long>(items, g->sm_count);
+  bool ok;
+  if (c.padded == 128) {
+    if (c.k_bits == 4 && c.v_bits == 2) ok = launch_stream_t<4, 16, 2, 8>(g, a, grid);
+    else if (c.k_bits == 4 && c.v_bits == 4) ok = launch_stream_t<4, 16, 4, 16>(g, a, grid);
+    else if (c.k_bits == 2 && c.v_bits == 2) ok = launch_stream_t<2, 8, 2, 8>(g, a, grid);
+    else ok = launch_stream_t<2, 8, 4, 16>(g, a, grid);
+  } else {
+    ok = launch_stream_t<4, 8, 4, 8>(g, a, grid);
+  }
+  if (!ok) return false;
+  if (a.n_splits > 1) {
+    merge_partials_kernel<<<items_base, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
+        a.partial, (size_t)items_base * partial_floats(c), a.n_splits, c, a.head0, a.nq,
+        want_partial_out ? partial_out : a.out, 0, want_partial_out ? 1 : 0);
+    ++g_launches;
+    CUDA_TRY(cudaGetLastError(), "compute (merge)");
+  }
+  return true;
+}
+
+bool launch_general_or_stream(Group *g, ComputeLaunch &a, bool want_partial_out, float *partial_out) {
+  const CacheView &c = g->c;
+  const int policy = g_policy.load();
+  const bool can_stream = !a.use_mirror && stream_supported(c);
+  if (can_stream && policy != 1) return launch_stream(g, a, want_partial_out, partial_out);
+  if (policy == 2) { set_error("compute: shape not covered by the streaming kernel"); return false; }
+  return launch_general(g, a, want_partial_out, partial_out);
+}
+
+// dq, dout on the device.  All heads of the call share `st`.
+bool compute_device(Group *g, const float *dq, float *dout, int head0, int heads_in_call, int nq, RingState st,
+                    bool partial_out) {
+  const CacheView &c = g->c;
+  if (heads_in_call <= 0 || nq <= 0) return true;
+  const size_t out_floats = (size_t)heads_in_call * nq * (partial_out ? partial_floats(c) : (size_t)c.dim);
+  if (st.size == 0) {
+    CUDA_TRY(cudaMemsetAsync(dout, 0, out_floats * 4, g->stream), "compute");
+    return true;
+  }
+  ComputeLaunch a{};
+  a.c = c; a.q = dq; a.out = dout; a.head0 = head0; a.heads_in_call = heads_in_call; a.nq = nq; a.n = st.size;
+  a.use_mirror = (c.hyb > 0 && st.size <= c.hyb && st.mirror == st.size) ? 1 : 0;
+  const bool quant = c.k_bits != 16 && c.v_bits != 16;
+  if (partial_out) return launch_general_or_stream(g, a, true, dout);
+  if (!a.use_mirror && c.v_mass > 0.f && quant) return launch_sparse(g, a);
+  return launch_general_or_stream(g, a, false, nullptr);
+}
+
+} // namespace
+
+// ===========================================================================
+// C ABI
+// ===========================================================================
+namespace {
+
+bool require_handle(const void *h, const char *op) {
+  if (h) return true;
+  set_error("%s: null handle", op);
+  return false;
+}
+bool require_pointer(const void *p, const char *op, const char *param) {
+  if (p) return true;
+  set_error("%s: null %s", op, param);
+  return false;
+}
+
+// One head, one token, host or device pointers.
+void append_one(Group *g, int head, const float *key, const float *val, const char *fn) {
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  const size_t vb = (size_t)g->c.dim * 4;
+  if (!ensure_stage(g, 2 * round_up(vb, 256), 2 * round_up(vb, 256))) return;
+  bool ok1, ok2;
+  const float *dk = to_device(g, key, vb, 0, ok1);
+  const float *dv = to_device(g, val, vb, round_up(vb, 256), ok2);
+  if (!ok1 || !ok2) return;
+  RingState st = g->state(head);
+  if (!append_device(g, dk, dv, head, 1, 1, (size_t)g->c.dim, st)) return;
+  RingState ns = advance(g->c, st, 1);
+  if (g->c.n_heads == 1) g->u = ns;
+  else { g->split_state(); g->per_head[head] = ns; g->try_unify(); }
+  // host buffers may be reused by the caller as soon as we return
+  if (ptr_kind(key) != PK_DEVICE || ptr_kind(val) != PK_DEVICE) {
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e));
+  }
+}
+
+// nq queries of one head.  Returns tokens used or -1.
+int compute_one(Group *g, int head, const float *queries, int nq, float *outs, const char *fn) {
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  RingState st = g->state(head);
+  if (nq == 0) return st.size;
+  const size_t qb = (size_t)nq * g->c.dim * 4;
+  const size_t off_out = round_up(qb, 256);
+  if (!ensure_stage(g, off_out + round_up(qb, 256), off_out + round_up(qb, 256))) return -1;
+  bool ok;
+  const float *dq = to_device(g, queries, qb, 0, ok);
+  if (!ok) return -1;
+  const PtrKind ok_kind = ptr_kind(outs);
+  float *dout = ok_kind == PK_DEVICE ? outs : reinterpret_cast<float *>(static_cast<char *>(g->d_stage) + off_out);
+  if (!compute_device(g, dq, dout, head, 1, nq, st, false)) return -1;
+  if (ok_kind != PK_DEVICE) {
+    void *hdst = ok_kind == PK_HOST_PINNED ? (void *)outs : (void *)(static_cast<char *>(g->h_stage) + off_out);
+    cudaError_t e = cudaMemcpyAsync(hdst, dout, qb, cudaMemcpyDeviceToHost, g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) { set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e)); return -1; }
+    if (ok_kind != PK_HOST_PINNED) memcpy(outs, hdst, qb);
+  } else if (ptr_kind(queries) != PK_DEVICE) {
+    cudaStreamSynchronize(g->stream);
+  }
+  return st.size;
+}
+
+void reset_group(Group *g) { // upstream core/adaptq_c_api.cpp:128-137: counters only, data stays
+  std::lock_guard<std::mutex> lk(g->mu);
+  g->uniform = true;
+  g->per_head.clear();
+  g->u = RingState{0, 0, 0};
+}
+
+size_t kv_bytes_group(Group *g) { // include/ring_buffer.h:93 summed over heads
+  std::lock_guard<std::mutex> lk(g->mu);
+  const size_t per_tok = (size_t)g->c.k_row + g->c.v_row;
+  if (g->uniform) return (size_t)g->u.size * per_tok * g->c.n_heads;
+  size_t t = 0;
+  for (auto &s : g->per_head) t += (size_t)s.size * per_tok;
+  return t;
+}
+
+} // namespace
+
+extern "C" {
+
+adaptq_ctx_t adaptq_create(int dim, int k_bits, int v_bits, int capacity, uint64_t seed, float v_mass,
+                           int hybrid_thresh) {
+  return create_group("adaptq_create", "adaptq_create: invalid dimensions or capacity", 1, &seed, dim, k_bits, v_bits,
+                      capacity, v_mass, hybrid_thresh, true);
+}
+
+void adaptq_destroy(adaptq_ctx_t h) { free_group(as_group(h)); }
+
+void adaptq_append(adaptq_ctx_t h, const float *key, const float *val, int /*token_pos*/) {
+  if (!require_handle(h, "adaptq_append") || !require_pointer(key, "adaptq_append", "key") ||
+      !require_pointer(val, "adaptq_append", "val"))
+    return;
+  Group *g = as_group(h);
+  if (!g) { set_error("adaptq_append: not a live handle"); return; }
+  append_one(g, 0, key, val, "adaptq_append");
+}
+
+int adaptq_compute(adaptq_ctx_t h, const float *query, float *out) {
+  if (!require_handle(h, "adaptq_compute") || !require_pointer(query, "adaptq_compute", "query") ||
+      !require_pointer(out, "adaptq_compute", "out"))
+    return -1;
+  Group *g = as_group(h);
+  if (!g) { set_error("adaptq_compute: not a live handle"); return -1; }
+  return compute_one(g, 0, query, 1, out, "adaptq_compute");
+}
+
+int adaptq_compute_batch(adaptq_ctx_t h, const float *queries, int num_queries, float *outs) {
+  if (!require_handle(h, "adaptq_compute_batch")) return -1;
+  if (num_queries < 0) { set_error("adaptq_compute_batch: negative num_queries"); return -1; }
+  if (num_queries > 0 && (!require_pointer(queries, "adaptq_compute_batch", "queries") ||
+                          !require_pointer(outs, "adaptq_compute_batch", "outs")))
+    return -1;
+  Group *g = as_group(h);
+  if (!g) { set_error("adaptq_compute_batch: not a live handle"); return -1; }
+  return compute_one(g, 0, queries, num_queries, outs, "adaptq_compute_batch");
+}
+
+void adaptq_reset(adaptq_ctx_t h) {
+  if (!require_handle(h, "adaptq_reset")) return;
+  Group *g = as_group(h);
+  if (!g) { set_error("adaptq_reset: not a live handle"); return; }
+  reset_group(g);
+  clear_error();
+}
+
+size_t adaptq_kv_bytes(adaptq_ctx_t h) {
+  if (!require_handle(h, "adaptq_kv_bytes")) return 0;
+  Group *g = as_group(h);
+  return g ? kv_bytes_group(g) : 0;
+}
+
+adaptq_mha_t adaptq_mha_create(int n_heads, int dim, int k_bits, int v_bits, int capacity, uint64_t base_seed,
+                               float v_mass, int hybrid_thresh) {
+  if (n_heads <= 0) { set_error("adaptq_mha_create: invalid parameters"); return nullptr; }
+  std::vector<uint64_t> seeds((size_t)n_heads);
+  for (int i = 0; i < n_heads; ++i) seeds[i] = base_seed ^ ((uint64_t)i * 0xDEADBEEFCAFEULL);
+  return create_group("adaptq_mha_create", "adaptq_mha_create: invalid parameters", n_heads, seeds.data(), dim, k_bits,
+                      v_bits, capacity, v_mass, hybrid_thresh, false);
+}
+
+adaptq_mha_t adaptq_mha_create_seeded(int n_heads, const uint64_t *seeds, int dim, int k_bits, int v_bits,
+                                      int capacity, float v_mass, int hybrid_thresh) {
+  if (n_heads <= 0 || !seeds) { set_error("adaptq_mha_create_seeded: invalid parameters"); return nullptr; }
+  return create_group("adaptq_mha_create_seeded", "adaptq_mha_create_seeded: invalid parameters", n_heads, seeds, dim,
+                      k_bits, v_bits, capacity, v_mass, hybrid_thresh, false);
+}
+
+void adaptq_mha_destroy(adaptq_mha_t h) { free_group(as_group(h)); }
+
+#define MHA_PROLOGUE(fn, fail)                                                     \
+  if (!require_handle(h, fn)) return fail;                                         \
+  Group *g = as_group(h);                                                          \
+  if (!g) { set_error("%s: not a live handle", fn); return fail; }
+
+void adaptq_mha_append(adaptq_mha_t h, int head_idx, const float *key, const float *val, int /*token_pos*/) {
+  MHA_PROLOGUE("adaptq_mha_append", )
+  if (head_idx < 0 || head_idx >= g->c.n_heads) { set_error("adaptq_mha_append: head_idx out of range"); return; }
+  if (!require_pointer(key, "adaptq_mha_append", "key") || !require_pointer(val, "adaptq_mha_append", "val")) return;
+  clear_error();
+  append_one(g, head_idx, key, val, "adaptq_mha_append");
+}
+
+int adaptq_mha_compute(adaptq_mha_t h, int head_idx, const float *query, float *out) {
+  MHA_PROLOGUE("adaptq_mha_compute", -1)
+  if (head_idx < 0 || head_idx >= g->c.n_heads) { set_error("adaptq_mha_compute: head_idx out of range"); return -1; }
+  if (!require_pointer(query, "adaptq_mha_compute", "query") || !require_pointer(out, "adaptq_mha_compute", "out"))
+    return -1;
+  clear_error();
+  return compute_one(g, head_idx, query, 1, out, "adaptq_mha_compute");
+}
+
+int adaptq_mha_compute_batch(adaptq_mha_t h, int head_idx, const float *queries, int num_queries, float *outs) {
+  MHA_PROLOGUE("adaptq_mha_compute_batch", -1)
+  if (head_idx < 0 || head_idx >= g->c.n_heads) {
+    set_error("adaptq_mha_compute_batch: head_idx out of range");
+    return -1;
+  }
+  if (num_queries < 0) { set_error("adaptq_mha_compute_batch: negative num_queries"); return -1; }
+  if (num_queries > 0 && (!require_pointer(queries, "adaptq_mha_compute_batch", "queries") ||
+                          !require_pointer(outs, "adaptq_mha_compute_batch", "outs")))
+    return -1;
+  clear_error();
+  return compute_one(g, head_idx, queries, num_queries, outs, "adaptq_mha_compute_batch");
+}
+
+void adaptq_mha_reset(adaptq_mha_t h) {
+  MHA_PROLOGUE("adaptq_mha_reset", )
+  reset_group(g);
+  clear_error();
+}
+
+size_t adaptq_mha_total_kv_bytes(adaptq_mha_t h) {
+  MHA_PROLOGUE("adaptq_mha_total_kv_bytes", 0)
+  return kv_bytes_group(g);
+}
+
+unsigned int adaptq_features(void) { return ADAPTQ_FEAT_HYBRID | ADAPTQ_FEAT_SPARSE_V | ADAPTQ_FEAT_CUDA_SM100; }
+const char *adaptq_version(void) { return "3.2.0-sm100a"; }
+
+// ---- batched additions ---------------------------------------------------------------
+
+int adaptq_mha_append_batch(adaptq_mha_t h, const float *keys, const float *vals, int n_tokens, int /*token_pos0*/) {
+  MHA_PROLOGUE("adaptq_mha_append_batch", -1)
+  if (n_tokens < 0) { set_error("adaptq_mha_append_batch: negative n_tokens"); return -1; }
+  if (n_tokens == 0) return 0;
+  if (!require_pointer(keys, "adaptq_mha_append_batch", "keys") || !require_pointer(vals, "adaptq_mha_append_batch", "vals"))
+    return -1;
+  clear_error();
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  const CacheView &c = g->c;
+  const size_t bytes = (size_t)n_tokens * c.n_heads * c.dim * 4, slot = round_up(bytes, 256);
+  const bool k_host = ptr_kind(keys) != PK_DEVICE, v_host = ptr_kind(vals) != PK_DEVICE;
+  const bool pageable = ptr_kind(keys) == PK_HOST_PAGEABLE || ptr_kind(vals) == PK_HOST_PAGEABLE;
+  if (k_host || v_host) {
+    if (!ensure_stage(g, 2 * slot, pageable ? 2 * slot : 0)) return -1;
+  }
+  bool ok1 = true, ok2 = true;
+  const float *dk = k_host ? to_device(g, keys, bytes, 0, ok1) : keys;
+  const float *dv = v_host ? to_device(g, vals, bytes, slot, ok2) : vals;
+  if (!ok1 || !ok2) return -1;
+  const size_t tstride = (size_t)c.n_heads * c.dim;
+  if (g->uniform) {
+    if (!append_device(g, dk, dv, 0, c.n_heads, n_tokens, tstride, g->u)) return -1;
+    g->u = advance(c, g->u, n_tokens);
+  } else {
+    for (int hd = 0; hd < c.n_heads; ++hd) {
+      if (!append_device(g, dk + (size_t)hd * c.dim, dv + (size_t)hd * c.dim, hd, 1, n_tokens, tstride, g->per_head[hd]))
+        return -1;
+      g->per_head[hd] = advance(c, g->per_head[hd], n_tokens);
+    }
+    g->try_unify();
+  }
+  if (k_host || v_host) {
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) { set_error("adaptq_mha_append_batch: CUDA error: %s", cudaGetErrorString(e)); return -1; }
+  }
+  return 0;
+}
+
+static int compute_all_impl(Group *g, const float *queries, int qph, float *outs, bool partial, const char *fn) {
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  const CacheView &c = g->c;
+  const size_t qb = (size_t)c.n_heads * qph * c.dim * 4;
+  const size_t ob = (size_t)c.n_heads * qph * (partial ? partial_floats(c) : (size_t)c.dim) * 4;
+  const size_t off_out = round_up(qb, 256);
+  const PtrKind qk = ptr_kind(queries), okd = ptr_kind(outs);
+  if (qk != PK_DEVICE || okd != PK_DEVICE) {
+    const bool pageable = qk == PK_HOST_PAGEABLE || okd == PK_HOST_PAGEABLE;
+    if (!ensure_stage(g, off_out + round_up(ob, 256), pageable ? off_out + round_up(ob, 256) : 0)) return -1;
+  }
+  bool ok = true;
+  const float *dq = qk == PK_DEVICE ? queries : to_device(g, queries, qb, 0, ok);
+  if (!ok) return -1;
+  float *dout = okd == PK_DEVICE ? outs : reinterpret_cast<float *>(static_cast<char *>(g->d_stage) + off_out);
+  int max_n = 0;
+  if (g->uniform) {
+    if (!compute_device(g, dq, dout, 0, c.n_heads, qph, g->u, partial)) return -1;
+    max_n = g->u.size;
+  } else {
+    const size_t per_head_out = (size_t)qph * (partial ? partial_floats(c) : (size_t)c.dim);
+    for (int hd = 0; hd < c.n_heads; ++hd) {
+      if (!compute_device(g, dq + (size_t)hd * qph * c.dim, dout + (size_t)hd * per_head_out, hd, 1, qph, g->per_head[hd], partial))
+        return -1;
+      max_n = std::max(max_n, g->per_head[hd].size);
+    }
+  }
+  if (okd != PK_DEVICE) {
+    void *hdst = okd == PK_HOST_PINNED ? (void *)outs : (void *)(static_cast<char *>(g->h_stage) + off_out);
+    cudaError_t e = cudaMemcpyAsync(hdst, dout, ob, cudaMemcpyDeviceToHost, g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) { set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e)); return -1; }
+    if (okd != PK_HOST_PINNED) memcpy(outs, hdst, ob);
+  } else if (qk != PK_DEVICE) {
+    cudaStreamSynchronize(g->stream);
+  }
+  return max_n;
+}
+
+int adaptq_mha_compute_all(adaptq_mha_t h, const float *queries, int queries_per_head, float *outs) {
+  MHA_PROLOGUE("adaptq_mha_compute_all", -1)
+  if (queries_per_head < 0) { set_error("adaptq_mha_compute_all: negative queries_per_head"); return -1; }
+  if (queries_per_head == 0) return g->uniform ? g->u.size : 0;
+  if (!require_pointer(queries, "adaptq_mha_compute_all", "queries") || !require_pointer(outs, "adaptq_mha_compute_all", "outs"))
+    return -1;
+  clear_error();
+  return compute_all_impl(g, queries, queries_per_head, outs, false, "adaptq_mha_compute_all");
+}
+
+int adaptq_mha_partial_floats(adaptq_mha_t h) {
+  MHA_PROLOGUE("adaptq_mha_partial_floats", -1)
+  return (int)partial_floats(g->c);
+}
+
+int adaptq_mha_compute_partial(adaptq_mha_t h, const float *queries, int queries_per_head, float *partials) {
+  MHA_PROLOGUE("adaptq_mha_compute_partial", -1)
+  if (queries_per_head <= 0) { set_error("adaptq_mha_compute_partial: queries_per_head must be positive"); return -1; }
+  if (!require_pointer(queries, "adaptq_mha_compute_partial", "queries") ||
+      !require_pointer(partials, "adaptq_mha_compute_partial", "partials"))
+    return -1;
+  const CacheView &c = g->c;
+  if (c.v_mass > 0.f || c.hyb > 0 || c.k_bits == 16 || c.v_bits == 16) {
+    set_error("adaptq_mha_compute_partial: needs dense V, no hybrid window and quantized K and V");
+    return -1;
+  }
+  clear_error();
+  return compute_all_impl(g, queries, queries_per_head, partials, true, "adaptq_mha_compute_partial");
+}
+
+int adaptq_mha_merge_partials(adaptq_mha_t h, const float *partials, int n_parts, int queries_per_head, float *outs) {
+  MHA_PROLOGUE("adaptq_mha_merge_partials", -1)
+  if (n_parts <= 0 || queries_per_head <= 0) { set_error("adaptq_mha_merge_partials: counts must be positive"); return -1; }
+  if (!require_pointer(partials, "adaptq_mha_merge_partials", "partials") ||
+      !require_pointer(outs, "adaptq_mha_merge_partials", "outs"))
+    return -1;
+  clear_error();
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  const CacheView &c = g->c;
+  const int items = c.n_heads * queries_per_head;
+  const size_t pb = (size_t)n_parts * items * partial_floats(c) * 4, ob = (size_t)items * c.dim * 4;
+  const size_t off_out = round_up(pb, 256);
+  const PtrKind pk = ptr_kind(partials), okd = ptr_kind(outs);
+  if (pk != PK_DEVICE || okd != PK_DEVICE) {
+    const bool pageable = pk == PK_HOST_PAGEABLE || okd == PK_HOST_PAGEABLE;
+    if (!ensure_stage(g, off_out + round_up(ob, 256), pageable ? off_out + round_up(ob, 256) : 0)) return -1;
+  }
+  bool ok = true;
+  const float *dp = pk == PK_DEVICE ? partials : to_device(g, partials, pb, 0, ok);
+  if (!ok) return -1;
+  float *dout = okd == PK_DEVICE ? outs : reinterpret_cast<float *>(static_cast<char *>(g->d_stage) + off_out);
+  merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
+      dp, (size_t)items * partial_floats(c), n_parts, c, 0, queries_per_head, dout, 0, 0);
+  ++g_launches;
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && okd != PK_DEVICE) {
+    void *hdst = okd == PK_HOST_PINNED ? (void *)outs : (void *)(static_cast<char *>(g->h_stage) + off_out);
+    e = cudaMemcpyAsync(hdst, dout, ob, cudaMemcpyDeviceToHost, g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e == cudaSuccess && okd != PK_HOST_PINNED) memcpy(outs, hdst, ob);
+  } else if (e == cudaSuccess && pk != PK_DEVICE) {
+    e = cudaStreamSynchronize(g->stream);
+  }
+  if (e != cudaSuccess) { set_error("adaptq_mha_merge_partials: CUDA error: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+int adaptq_mha_set_stream(adaptq_mha_t h, void *cuda_stream) {
+  MHA_PROLOGUE("adaptq_mha_set_stream", -1)
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  cudaStreamSynchronize(g->stream);
+  g->stream = static_cast<cudaStream_t>(cuda_stream);
+  return 0;
+}
+
+int adaptq_mha_synchronize(adaptq_mha_t h) {
+  MHA_PROLOGUE("adaptq_mha_synchronize", -1)
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  return check_status(g, "adaptq_mha_synchronize") ? 0 : -1;
+}
+
+int adaptq_mha_info(adaptq_mha_t h, adaptq_mha_info_t *info) {
+  MHA_PROLOGUE("adaptq_mha_info", -1)
+  if (!require_pointer(info, "adaptq_mha_info", "info")) return -1;
+  const CacheView &c = g->c;
+  info->n_heads = c.n_heads; info->dim = c.dim; info->padded = c.padded; info->k_bits = c.k_bits; info->v_bits = c.v_bits;
+  info->capacity = c.cap; info->hybrid_thresh = c.hyb; info->k_row_bytes = c.k_row; info->v_row_bytes = c.v_row;
+  info->device = g->device; info->v_mass = c.v_mass; info->device_bytes = g->device_bytes;
+  return 0;
+}
+
+int adaptq_mha_export_head(adaptq_mha_t h, int head_idx, uint8_t *k_rows, uint8_t *v_rows, float *k_scale, float *v_scale,
+                           int8_t *signs, int *ring_head, int *ring_size, int *mirror_tokens) {
+  MHA_PROLOGUE("adaptq_mha_export_head", -1)
+  if (head_idx < 0 || head_idx >= g->c.n_heads) { set_error("adaptq_mha_export_head: head_idx out of range"); return -1; }
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  const CacheView &c = g->c;
+  cudaError_t e = cudaStreamSynchronize(g->stream);
+  auto d2h = [&](void *dst, const void *src, size_t n) {
+    if (e == cudaSuccess && dst && n) e = cudaMemcpy(dst, src, n, cudaMemcpyDeviceToHost);
+  };
+  d2h(k_rows, c.k_slab + (size_t)head_idx * c.k_stride, (size_t)c.cap * c.k_row);
+  d2h(v_rows, c.v_slab + (size_t)head_idx * c.v_stride, (size_t)c.cap * c.v_row);
+  d2h(k_scale, c.k_scale + (size_t)head_idx * c.s_stride, (size_t)c.cap * 4);
+  d2h(v_scale, c.v_scale + (size_t)head_idx * c.s_stride, (size_t)c.cap * 4);
+  if (e != cudaSuccess) { set_error("adaptq_mha_export_head: CUDA error: %s", cudaGetErrorString(e)); return -1; }
+  if (signs) {
+    std::vector<uint32_t> w((size_t)c.sign_words);
+    sign_words_for(g->seeds[head_idx], c.padded, w.data(), c.sign_words);
+    for (int i = 0; i < c.padded; ++i) signs[i] = ((w[i >> 5] >> (i & 31)) & 1u) ? -1 : 1;
+  }
+  RingState st = g->state(head_idx);
+  if (ring_head) *ring_head = st.head;
+  if (ring_size) *ring_size = st.size;
+  if (mirror_tokens) *mirror_tokens = st.mirror;
+  return 0;
+}
+
+} // extern "C"

@@ -1,0 +1,365 @@
+// Append kernels: FP32 vector -> (sign flip, Walsh-Hadamard, Lloyd-Max
+// quantisation, MSB-first bit packing) -> ring slot of the device cache.
+//
+// Replaces upstream AttentionHead::append_kv (attention/attention.cpp:338-366),
+// Quantizer::quantize_into / _quantize_core (core/quantizer.cpp:53-137),
+// fwht_forward (core/fwht.cpp:33-104), quantize_fast (core/codebook.cpp:119-144),
+// pack_indices (core/quantizer.cpp:156-225) and KVFlatBuffer::insert
+// (cache/ring_buffer.cpp:105-119).
+//
+// Bit-exactness: every floating-point step is issued as an individually
+// rounded IEEE operation in upstream's order (no FMA contraction): the norm
+// and the clip's sum of squares are strictly sequential chains over the
+// index, the butterflies run in stage order len = 1, 2, ... p/2, and the two
+// scalings by 1/sqrt(p) and sqrt(p) stay separate multiplies.
+#pragma once
+#include "common.cuh"
+
+namespace aq {
+
+struct AppendLaunch {
+  CacheView c;
+  const float *src; // token t, head head0+i at  src + t*src_token_stride + i*dim
+  size_t src_token_stride; // floats between consecutive tokens
+  int which;        // 0 = keys, 1 = values
+  int head0, heads_in_call, n_tokens;
+  int ring_head, ring_size, mirror_cnt; // state shared by the heads of this call
+  int head_major;
+  int *status;
+};
+
+struct ItemPlace {
+  bool store;  // write the packed row + scale
+  bool mirror; // write the FP32 mirror row
+  int h, t, slot;
+};
+
+// Where does work item g go?  Tokens that a later token of the same call
+// overwrites (n_tokens > capacity) are dropped, which keeps the parallel
+// writes race-free and matches the FIFO end state.
+__device__ __forceinline__ ItemPlace place_item(const AppendLaunch &a, long long g) {
+  ItemPlace p;
+  int hl;
+  if (a.head_major) {
+    hl = (int)(g / a.n_tokens);
+    p.t = (int)(g % a.n_tokens);
+  } else {
+    p.t = (int)(g / a.heads_in_call);
+    hl = (int)(g % a.heads_in_call);
+  }
+  p.h = a.head0 + hl;
+  const int cap = a.c.cap, T = a.n_tokens;
+  p.store = cap > 0 && p.t >= T - cap;
+  p.slot = cap > 0 ? (int)(((long long)a.ring_head + p.t) % cap) : 0;
+  // Mirror rule of upstream attention/attention.cpp:354-365: push while the
+  // ring has not started evicting and the mirror is short of hybrid_thresh;
+  // the first eviction clears it, so a call that ends past capacity writes none.
+  bool call_evicts = (long long)a.ring_size + T > cap;
+  p.mirror = a.c.hyb > 0 && !call_evicts && (a.mirror_cnt + p.t < a.c.hyb);
+  return p;
+}
+
+__device__ __forceinline__ const float *item_src(const AppendLaunch &a, const ItemPlace &p) {
+  return a.src + (size_t)p.t * a.src_token_stride + (size_t)(p.h - a.head0) * a.c.dim;
+}
+
+// ---------------------------------------------------------------------------
+// Register-resident path: one thread owns one vector (P floats in registers).
+// ---------------------------------------------------------------------------
+template <int P, int BITS>
+__device__ __forceinline__ float quantize_row_regs(float (&x)[P], const uint32_t (&sg)[(P + 31) / 32],
+                                                   uint32_t (&w)[(P * BITS + 31) / 32]) {
+  // L2 norm: sequential, multiply and add rounded separately (core/quantizer.cpp:59-66)
+  float norm = 0.f;
+#pragma unroll
+  for (int i = 0; i < P; ++i) norm = __fadd_rn(norm, __fmul_rn(x[i], x[i]));
+  norm = __fsqrt_rn(__fadd_rn(norm, 1e-12f));
+  const float inv = __fdiv_rn(1.0f, norm);
+  // normalise, then the Rademacher sign (a sign-bit XOR equals the multiply by +-1)
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    float v = __fmul_rn(x[i], inv);
+    uint32_t flip = (sg[i >> 5] << (31 - (i & 31))) & 0x80000000u;
+    x[i] = __uint_as_float(__float_as_uint(v) ^ flip);
+  }
+  // butterflies, core/fwht.cpp:36-57
+#pragma unroll
+  for (int len = 1; len < P; len <<= 1) {
+#pragma unroll
+    for (int i = 0; i < P; i += (len << 1)) {
+#pragma unroll
+      for (int j = 0; j < len; ++j) {
+        float a = x[i + j], b = x[i + j + len];
+        x[i + j] = __fadd_rn(a, b);
+        x[i + j + len] = __fsub_rn(a, b);
+      }
+    }
+  }
+  const float sq = __fsqrt_rn((float)P);
+  const float isq = __fdiv_rn(1.0f, sq);
+  // x * (1/sqrt p) [core/fwht.cpp:60-65]  then * sqrt p [core/quantizer.cpp:73-75]
+  float sum2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    x[i] = __fmul_rn(__fmul_rn(x[i], isq), sq);
+    sum2 = __fadd_rn(sum2, __fmul_rn(x[i], x[i]));
+  }
+  // +-3 sigma clip, core/quantizer.cpp:81-89
+  const float sigma = __fsqrt_rn(__fadd_rn(__fdiv_rn(sum2, (float)P), 1e-12f));
+  const float clip = __fmul_rn(3.0f, sigma);
+  const float nclip = -clip;
+#pragma unroll
+  for (int i = 0; i < (P * BITS + 31) / 32; ++i) w[i] = 0;
+  if (BITS == 4) {
+#pragma unroll
+    for (int i = 0; i < P; i += 8) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float v = x[i + k];
+        if (v > clip) v = clip;
+        if (v < nclip) v = nclip;
+        uint32_t q = (uint32_t)quantize_value<4>(v);
+        // byte k/2 of the word, high nibble first
+        word |= q << (8 * (k >> 1) + ((k & 1) ? 0 : 4));
+      }
+      w[i >> 3] = word;
+    }
+  } else if (BITS == 2) {
+#pragma unroll
+    for (int i = 0; i < P; i += 16) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        float v = x[i + k];
+        if (v > clip) v = clip;
+        if (v < nclip) v = nclip;
+        uint32_t q = (uint32_t)quantize_value<2>(v);
+        word |= q << (8 * (k >> 2) + (6 - 2 * (k & 3)));
+      }
+      w[i >> 4] = word;
+    }
+  } else { // 3 bits: 8 indices -> 3 bytes, big-endian bit order
+#pragma unroll
+    for (int i = 0; i < P; i += 32) {
+      uint32_t r[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t v24 = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          float v = x[i + g * 8 + k];
+          if (v > clip) v = clip;
+          if (v < nclip) v = nclip;
+          v24 |= (uint32_t)quantize_value<3>(v) << (21 - 3 * k);
+        }
+        // memory image of the three bytes (p0 first) as a little-endian integer
+        r[g] = __byte_perm(v24, 0, 0x3012);
+      }
+      w[(i >> 5) * 3 + 0] = r[0] | (r[1] << 24);
+      w[(i >> 5) * 3 + 1] = (r[1] >> 8) | (r[2] << 16);
+      w[(i >> 5) * 3 + 2] = (r[2] >> 16) | (r[3] << 8);
+    }
+  }
+  return norm;
+}
+
+// One block = THREADS vectors per tile; rows arrive in shared memory through
+// per-row bulk (TMA) copies, each thread then pulls its row into registers,
+// and the next tile's copies are issued before the arithmetic starts.
+template <int P, int BITS, int THREADS>
+__global__ void __launch_bounds__(THREADS, (P == 128 ? 3 : 4))
+append_rows_kernel(const AppendLaunch a) {
+  constexpr int PITCH = P + 4; // floats; +16 B keeps 128-bit row reads conflict-free
+  extern __shared__ __align__(128) unsigned char smem_rows[];
+  float *tile = reinterpret_cast<float *>(smem_rows);
+  __shared__ __align__(8) uint64_t bar;
+
+  const int tid = threadIdx.x;
+  const long long n_items = (long long)a.heads_in_call * a.n_tokens;
+  const long long n_tiles = (n_items + THREADS - 1) / THREADS;
+  const int dim = a.c.dim;
+  const uint32_t row_bytes_in = (uint32_t)dim * 4u;
+  float *my_row = tile + (size_t)tid * PITCH;
+
+  if (tid == 0) {
+    mbar_init(&bar, THREADS);
+    fence_barrier_init();
+  }
+  // zero the padding columns once (dim < P); bulk copies never touch them
+  for (int i = dim; i < P; ++i) my_row[i] = 0.f;
+  __syncthreads();
+
+  auto issue = [&](long long tile_idx) {
+    long long g = tile_idx * THREADS + tid;
+    if (g < n_items) {
+      ItemPlace p = place_item(a, g);
+      if (p.store || p.mirror) {
+        mbar_expect_tx(&bar, row_bytes_in);
+        bulk_g2s(my_row, item_src(a, p), row_bytes_in, &bar);
+        return;
+      }
+    }
+    mbar_arrive(&bar);
+  };
+
+  long long tile_idx = blockIdx.x;
+  if (tile_idx < n_tiles) issue(tile_idx);
+  uint32_t parity = 0;
+  for (; tile_idx < n_tiles; tile_idx += gridDim.x) {
+    if (!mbar_wait(&bar, parity)) {
+      if (tid == 0) atomicExch(a.status, 1);
+      return;
+    }
+    parity ^= 1u;
+    const long long g = tile_idx * THREADS + tid;
+    ItemPlace p;
+    p.store = p.mirror = false;
+    if (g < n_items) p = place_item(a, g);
+    float x[P];
+    if (p.store || p.mirror) {
+      const float4 *r4 = reinterpret_cast<const float4 *>(my_row);
+#pragma unroll
+      for (int i = 0; i < P / 4; ++i) {
+        float4 v = r4[i];
+        x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+      }
+    }
+    __syncthreads(); // every row has been read; the tile buffer is free
+    const long long next = tile_idx + gridDim.x;
+    if (next < n_tiles) {
+      fence_proxy_async();
+      issue(next);
+    }
+    if (p.mirror) {
+      float4 *m4 = reinterpret_cast<float4 *>(a.c.mirror + (size_t)p.h * a.c.mirror_stride +
+                                              (size_t)p.slot * 2 * dim + (a.which ? dim : 0));
+#pragma unroll
+      for (int i = 0; i < P / 4; ++i)
+        if (4 * i < dim) m4[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+    }
+    if (!p.store) continue;
+    const CacheView &c = a.c;
+    uint8_t *slab = a.which ? c.v_slab : c.k_slab;
+    const size_t stride = a.which ? c.v_stride : c.k_stride;
+    float *scale = (a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride + p.slot;
+    if constexpr (BITS == 16) {
+      float4 *dst = reinterpret_cast<float4 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4));
+#pragma unroll
+      for (int i = 0; i < P / 4; ++i) dst[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+      *scale = 1.0f;
+    } else {
+      constexpr int QB = (BITS == 16) ? 4 : BITS;
+      constexpr int NW = (P * QB + 31) / 32;
+      uint32_t sg[(P + 31) / 32];
+#pragma unroll
+      for (int i = 0; i < (P + 31) / 32; ++i) sg[i] = c.signs[(size_t)p.h * c.sign_words + i];
+      uint32_t w[NW];
+      float norm = quantize_row_regs<P, QB>(x, sg, w);
+      uint8_t *row = slab + (size_t)p.h * stride + (size_t)p.slot * (NW * 4);
+      if ((NW * 4) % 16 == 0) {
+        uint4 *d4 = reinterpret_cast<uint4 *>(row);
+#pragma unroll
+        for (int i = 0; i < NW / 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      } else {
+        uint2 *d2 = reinterpret_cast<uint2 *>(row);
+#pragma unroll
+        for (int i = 0; i < NW / 2; ++i) d2[i] = make_uint2(w[2 * i], w[2 * i + 1]);
+      }
+      *scale = norm;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// General path: one warp per vector, the vector lives in shared memory.
+// Any dim with padded <= 1024, any alignment.  Same arithmetic, same order.
+// ---------------------------------------------------------------------------
+constexpr int GEN_WARPS = 4;
+
+__global__ void __launch_bounds__(GEN_WARPS * 32) append_general_kernel(const AppendLaunch a) {
+  extern __shared__ __align__(16) unsigned char smem_gen[];
+  unsigned char *smem_raw = smem_gen;
+  const int P = a.c.padded, dim = a.c.dim;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float *buf = reinterpret_cast<float *>(smem_raw) + (size_t)warp * P;
+  const CacheView &c = a.c;
+  const int bits = a.which ? c.v_bits : c.k_bits;
+  const int rowb = a.which ? c.v_row : c.k_row;
+  const long long n_items = (long long)a.heads_in_call * a.n_tokens;
+
+  for (long long g = (long long)blockIdx.x * GEN_WARPS + warp; g < n_items; g += (long long)gridDim.x * GEN_WARPS) {
+    ItemPlace p = place_item(a, g);
+    if (!p.store && !p.mirror) continue;
+    const float *src = item_src(a, p);
+    for (int i = lane; i < P; i += 32) buf[i] = i < dim ? src[i] : 0.f;
+    __syncwarp();
+    if (p.mirror) {
+      float *m = c.mirror + (size_t)p.h * c.mirror_stride + (size_t)p.slot * 2 * dim + (a.which ? dim : 0);
+      for (int i = lane; i < dim; i += 32) m[i] = buf[i];
+    }
+    if (!p.store) { __syncwarp(); continue; }
+    uint8_t *row = (a.which ? c.v_slab : c.k_slab) + (size_t)p.h * (a.which ? c.v_stride : c.k_stride) + (size_t)p.slot * rowb;
+    float *scale = (a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride + p.slot;
+    if (bits == 16) {
+      float *dst = reinterpret_cast<float *>(row);
+      for (int i = lane; i < P; i += 32) dst[i] = buf[i];
+      if (lane == 0) *scale = 1.0f;
+      __syncwarp();
+      continue;
+    }
+    const uint32_t *sg = c.signs + (size_t)p.h * c.sign_words;
+    float norm = 0.f;
+    if (lane == 0) {
+      for (int i = 0; i < dim; ++i) norm = __fadd_rn(norm, __fmul_rn(buf[i], buf[i]));
+      norm = __fsqrt_rn(__fadd_rn(norm, 1e-12f));
+    }
+    norm = __shfl_sync(0xffffffffu, norm, 0);
+    const float inv = __fdiv_rn(1.0f, norm);
+    for (int i = lane; i < P; i += 32) buf[i] = __fmul_rn(__fmul_rn(buf[i], inv), sign_of(sg, i));
+    __syncwarp();
+    for (int len = 1; len < P; len <<= 1) {
+      for (int t = lane; t < (P >> 1); t += 32) {
+        int i = ((t / len) * (len << 1)) + (t % len);
+        float x0 = buf[i], x1 = buf[i + len];
+        buf[i] = __fadd_rn(x0, x1);
+        buf[i + len] = __fsub_rn(x0, x1);
+      }
+      __syncwarp();
+    }
+    const float sq = __fsqrt_rn((float)P), isq = __fdiv_rn(1.0f, sq);
+    for (int i = lane; i < P; i += 32) buf[i] = __fmul_rn(__fmul_rn(buf[i], isq), sq);
+    __syncwarp();
+    float clip = 0.f;
+    if (lane == 0) {
+      float sum2 = 0.f;
+      for (int i = 0; i < P; ++i) sum2 = __fadd_rn(sum2, __fmul_rn(buf[i], buf[i]));
+      clip = __fmul_rn(3.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum2, (float)P), 1e-12f)));
+    }
+    clip = __shfl_sync(0xffffffffu, clip, 0);
+    auto qat = [&](int i) -> uint32_t {
+      float v = buf[i];
+      if (v > clip) v = clip;
+      if (v < -clip) v = -clip;
+      return (uint32_t)quantize_value_rt(v, bits);
+    };
+    if (bits == 4) {
+      for (int m = lane; m < P / 2; m += 32) row[m] = (uint8_t)((qat(2 * m) << 4) | qat(2 * m + 1));
+    } else if (bits == 2) {
+      for (int m = lane; m < P / 4; m += 32)
+        row[m] = (uint8_t)((qat(4 * m) << 6) | (qat(4 * m + 1) << 4) | (qat(4 * m + 2) << 2) | qat(4 * m + 3));
+    } else {
+      for (int g3 = lane; g3 < P / 8; g3 += 32) {
+        uint32_t v24 = 0;
+        for (int k = 0; k < 8; ++k) v24 |= qat(g3 * 8 + k) << (21 - 3 * k);
+        row[g3 * 3] = (uint8_t)(v24 >> 16);
+        row[g3 * 3 + 1] = (uint8_t)(v24 >> 8);
+        row[g3 * 3 + 2] = (uint8_t)v24;
+      }
+    }
+    if (lane == 0) *scale = norm;
+    __syncwarp();
+  }
+}
+
+} // namespace aq

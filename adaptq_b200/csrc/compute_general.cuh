@@ -1,0 +1,342 @@
+// General-purpose decode-attention kernels: every bit width (2/3/4/16 for K
+// and V), every padded dimension up to 1024, the hybrid FP32 window, split-KV
+// partials and their merge, and the sparse-V selection.
+//
+// Replaces upstream AttentionHead::compute (attention/attention.cpp:480-660):
+// hybrid branch :491-523, query rotation :526-550, K16 branch :565-600,
+// quantised branch (compute_avx2) :373-474, inverse transform
+// (core/fwht.cpp:106-134).  Scores come straight from the packed indices
+// through a q[j]*centroid table in shared memory; nothing is dequantised.
+//
+// A softmax over a set is independent of the order of the set, so the dense
+// paths walk the ring's physical slots 0..n-1 (every slot below `size` is
+// live, wrapped or not) instead of upstream's oldest-to-newest order.
+#pragma once
+#include "common.cuh"
+
+namespace aq {
+
+constexpr int CG_THREADS = 256;
+constexpr int CG_WARPS = CG_THREADS / 32;
+
+struct ComputeLaunch {
+  CacheView c;
+  const float *q; // [heads_in_call][nq][dim]
+  float *out;     // [heads_in_call][nq][dim]            (mode 0)
+  float *partial; // [n_splits][heads_in_call*nq][2+P]  (mode 1)
+  float *weights; // [heads_in_call][nq][w_stride]       (mode 2: normalised softmax weights)
+  int w_stride;
+  int head0, heads_in_call, nq;
+  int n;        // live tokens (same for every head of the call)
+  int use_mirror;
+  int n_splits, span; // tokens per split
+  int chunk;          // tokens per shared-memory pass
+  int mode;
+};
+
+// Shared-memory carve-up (floats): qr[P] | vec[P] | red[64] | lut[P*CBK or 0] | sc[chunk]
+__host__ __device__ inline size_t cg_smem_floats(int P, int k_quant_levels, int chunk) {
+  return (size_t)P * 2 + 64 + (size_t)P * k_quant_levels + chunk;
+}
+
+__device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = is_max ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = red[0];
+  for (int i = 1; i < CG_WARPS; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+  return r;
+}
+
+__global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const ComputeLaunch a) {
+  extern __shared__ __align__(16) unsigned char smem_gen[];
+  unsigned char *smem_raw = smem_gen;
+  const CacheView &c = a.c;
+  const int P = c.padded, dim = c.dim;
+  const int split = blockIdx.x, hl = blockIdx.y, qi = blockIdx.z;
+  const int h = a.head0 + hl;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  const bool mirror = a.use_mirror != 0;
+  const bool k_f32 = mirror || c.k_bits == 16;
+  const bool v_f32 = mirror || c.v_bits == 16;
+  const int kcb = k_f32 ? 0 : (1 << c.k_bits);
+
+  float *qr = reinterpret_cast<float *>(smem_raw);
+  float *vec = qr + P;
+  float *red = vec + P;
+  float *lut = red + 64;
+  float *sc = lut + (size_t)P * kcb;
+
+  const float *q = a.q + ((size_t)hl * a.nq + qi) * dim;
+  const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
+
+  // ---- query: raw for FP32 keys, rotated for quantised keys ---------------
+  for (int i = tid; i < P; i += CG_THREADS) qr[i] = i < dim ? q[i] : 0.f;
+  __syncthreads();
+  float attn_s = 1.f / sqrtf((float)dim);
+  const float isp = 1.f / sqrtf((float)P);
+  if (!k_f32) {
+    float part = 0.f;
+    for (int i = tid; i < dim; i += CG_THREADS) part += qr[i] * qr[i];
+    float qn = sqrtf(block_reduce(part, red, false) + 1e-12f);
+    float inv = 1.f / qn;
+    for (int i = tid; i < P; i += CG_THREADS) qr[i] = qr[i] * inv * sign_of(sg, i);
+    __syncthreads();
+    block_butterflies(qr, P);
+    const float m = sqrtf((float)P) * qn;
+    for (int i = tid; i < P; i += CG_THREADS) qr[i] = qr[i] * isp * m;
+    __syncthreads();
+    attn_s = 1.f / (sqrtf((float)dim) * (float)P);
+    // table[level][j] = q_rot[j] * centroid[level]; column j sits in bank j%32
+    const float *cb = c_cb[c.k_bits - 2];
+    for (int i = tid; i < P * kcb; i += CG_THREADS) lut[i] = qr[i % P] * cb[i / P];
+    __syncthreads();
+  }
+
+  const uint8_t *kbase = c.k_slab + (size_t)h * c.k_stride;
+  const uint8_t *vbase = c.v_slab + (size_t)h * c.v_stride;
+  const float *ksc = c.k_scale + (size_t)h * c.s_stride;
+  const float *vsc = c.v_scale + (size_t)h * c.s_stride;
+  const float *mir = mirror ? c.mirror + (size_t)h * c.mirror_stride : nullptr;
+
+  const int t_begin = min(a.n, split * a.span), t_end = min(a.n, t_begin + a.span);
+
+  // Each thread owns output columns j = jcol + r*CG_THREADS of token group tg.
+  const int TG = P < CG_THREADS ? CG_THREADS / P : 1;
+  const int jcol = P < CG_THREADS ? tid % P : tid;
+  const int tg = P < CG_THREADS ? tid / P : 0;
+  constexpr int MAXR = 4; // P <= 1024
+  float acc[MAXR] = {0.f, 0.f, 0.f, 0.f};
+  float run_m = -INFINITY, run_l = 0.f;
+  const float *vcb = v_f32 ? nullptr : c_cb[c.v_bits - 2];
+
+  for (int t0 = t_begin; t0 < t_end; t0 += a.chunk) {
+    const int cn = min(a.chunk, t_end - t0);
+    // ---- scores ----------------------------------------------------------
+    for (int i = warp; i < cn; i += CG_WARPS) {
+      const int s = t0 + i;
+      float sum = 0.f;
+      if (k_f32) {
+        const float *kr = mirror ? mir + (size_t)s * 2 * dim : reinterpret_cast<const float *>(kbase + (size_t)s * c.k_row);
+        for (int j = lane; j < dim; j += 32) sum += qr[j] * kr[j];
+      } else {
+        const uint8_t *kr = kbase + (size_t)s * c.k_row;
+        for (int j = lane; j < P; j += 32) sum += lut[unpack_at(kr, j, c.k_bits) * P + j];
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) sc[i] = k_f32 ? sum * attn_s : sum * attn_s * ksc[s];
+    }
+    __syncthreads();
+    if (a.mode == 2) { // raw logits out; normalised later by softmax_weights_kernel
+      float *w = a.weights + ((size_t)hl * a.nq + qi) * a.w_stride;
+      for (int i = tid; i < cn; i += CG_THREADS) w[t0 + i] = sc[i];
+      __syncthreads();
+      continue;
+    }
+    // ---- online softmax over this pass -------------------------------------
+    float mx = -INFINITY;
+    for (int i = tid; i < cn; i += CG_THREADS) mx = fmaxf(mx, sc[i]);
+    mx = block_reduce(mx, red, true);
+    const float new_m = fmaxf(run_m, mx);
+    const float rescale = (run_m == -INFINITY) ? 0.f : expf(run_m - new_m);
+    float ls = 0.f;
+    for (int i = tid; i < cn; i += CG_THREADS) {
+      float e = expf(sc[i] - new_m);
+      ls += e;
+      // fold the per-token V factor in once: w * vscale * (1/sqrt p)
+      sc[i] = v_f32 ? e : e * vsc[t0 + i] * isp;
+    }
+    ls = block_reduce(ls, red, false);
+    run_l = run_l * rescale + ls;
+    run_m = new_m;
+    __syncthreads();
+    // ---- V accumulation ------------------------------------------------------
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) {
+      const int j = jcol + r * CG_THREADS;
+      if (j >= P || (P < CG_THREADS && r > 0)) break;
+      float av = acc[r] * rescale;
+      for (int i = tg; i < cn; i += TG) {
+        const int s = t0 + i;
+        if (v_f32) {
+          if (j < dim) {
+            const float *vr = mirror ? mir + (size_t)s * 2 * dim + dim : reinterpret_cast<const float *>(vbase + (size_t)s * c.v_row);
+            av += sc[i] * vr[j];
+          }
+        } else {
+          av += sc[i] * vcb[unpack_at(vbase + (size_t)s * c.v_row, j, c.v_bits)];
+        }
+      }
+      acc[r] = av;
+    }
+    __syncthreads();
+  }
+  if (a.mode == 2) return;
+
+  // ---- fold token groups ------------------------------------------------------
+  // vec[j] = sum over token groups; TG groups of P columns fit CG_THREADS exactly
+  if (P < CG_THREADS) {
+    float *fold = sc; // chunk >= CG_THREADS floats is guaranteed by the host
+    fold[tid] = acc[0];
+    __syncthreads();
+    if (tid < P) {
+      float s = 0.f;
+      for (int g = 0; g < TG; ++g) s += fold[g * P + tid];
+      vec[tid] = s;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) {
+      const int j = jcol + r * CG_THREADS;
+      if (j < P) vec[j] = acc[r];
+    }
+  }
+  __syncthreads();
+
+  if (a.mode == 1) {
+    float *pp = a.partial + ((size_t)split * a.heads_in_call * a.nq + (size_t)hl * a.nq + qi) * (size_t)(2 + P);
+    if (tid == 0) { pp[0] = run_m; pp[1] = run_l; }
+    for (int j = tid; j < P; j += CG_THREADS) pp[2 + j] = vec[j];
+    return;
+  }
+  // ---- normalise, inverse transform, write ----------------------------------------
+  const float invl = 1.f / run_l;
+  float *o = a.out + ((size_t)hl * a.nq + qi) * dim;
+  if (v_f32) {
+    for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * invl;
+    return;
+  }
+  for (int j = tid; j < P; j += CG_THREADS) vec[j] *= invl;
+  __syncthreads();
+  block_butterflies(vec, P);
+  for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
+}
+
+// Merge n_parts split-KV partials per (head, query): rescale to the common
+// max, sum, normalise, one inverse transform.  parts laid out
+// [n_parts][items][2+P] with part stride `part_stride` floats.
+__global__ void __launch_bounds__(CG_THREADS) merge_partials_kernel(
+    const float *parts, size_t part_stride, int n_parts, CacheView c, int head0, int nq, float *out,
+    int v_f32, int to_partial) {
+  extern __shared__ __align__(16) unsigned char smem_gen[];
+  unsigned char *smem_raw = smem_gen;
+  float *vec = reinterpret_cast<float *>(smem_raw);
+  const int P = c.padded, dim = c.dim;
+  const int item = blockIdx.x; // hl*nq + qi
+  const int h = head0 + item / nq;
+  const int tid = threadIdx.x;
+  const float *base = parts + (size_t)item * (2 + P);
+  float M = -INFINITY;
+  for (int p = 0; p < n_parts; ++p) {
+    const float *pp = base + (size_t)p * part_stride;
+    if (pp[1] > 0.f) M = fmaxf(M, pp[0]);
+  }
+  float L = 0.f;
+  for (int p = 0; p < n_parts; ++p) {
+    const float *pp = base + (size_t)p * part_stride;
+    if (pp[1] > 0.f) L += pp[1] * expf(pp[0] - M);
+  }
+  const float invL = to_partial ? 1.f : 1.f / L;
+  for (int j = tid; j < P; j += CG_THREADS) {
+    float s = 0.f;
+    for (int p = 0; p < n_parts; ++p) {
+      const float *pp = base + (size_t)p * part_stride;
+      if (pp[1] > 0.f) s += pp[2 + j] * expf(pp[0] - M);
+    }
+    vec[j] = s * invL;
+  }
+  if (to_partial) { // one combined, still un-normalised partial per (head, query)
+    float *po = out + (size_t)item * (2 + P);
+    if (tid == 0) { po[0] = M; po[1] = L; }
+    for (int j = tid; j < P; j += CG_THREADS) po[2 + j] = vec[j];
+    return;
+  }
+  __syncthreads();
+  float *o = out + (size_t)item * dim;
+  if (v_f32) {
+    for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j];
+    return;
+  }
+  block_butterflies(vec, P);
+  const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
+  const float isp = 1.f / sqrtf((float)P);
+  for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
+}
+
+// ---------------------------------------------------------------------------
+// Sparse V (upstream attention/attention.cpp:448-473): the heaviest softmax
+// weights are accumulated, four at a time, until their running mass reaches
+// v_mass; the weights are not renormalised.
+// Step 1 (this kernel): logits -> weights e*(1/sum) in place, plus the token
+// index list for the sort.  One block per (head, query).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(CG_THREADS) softmax_weights_kernel(float *weights, int *order, int w_stride, int n) {
+  __shared__ float red[64];
+  float *w = weights + (size_t)blockIdx.x * w_stride;
+  int *o = order + (size_t)blockIdx.x * w_stride;
+  const int tid = threadIdx.x;
+  float mx = -1e30f;
+  for (int i = tid; i < n; i += CG_THREADS) mx = fmaxf(mx, w[i]);
+  mx = block_reduce(mx, red, true);
+  float s = 0.f;
+  for (int i = tid; i < n; i += CG_THREADS) {
+    float e = expf(w[i] - mx);
+    w[i] = e;
+    s += e;
+  }
+  s = block_reduce(s, red, false);
+  const float inv = 1.f / s;
+  for (int i = tid; i < n; i += CG_THREADS) {
+    w[i] *= inv;
+    o[i] = i;
+  }
+}
+
+// Step 3 (after a stable descending sort of (weight, token) per block):
+// find the cut exactly as upstream does -- blocks of four while four remain
+// and the mass is short, then singles -- and accumulate those V rows.
+__global__ void __launch_bounds__(CG_THREADS) sparse_accumulate_kernel(
+    const float *sorted_w, const int *sorted_tok, int w_stride, int n, CacheView c, int head0, int nq, float *out) {
+  extern __shared__ __align__(16) unsigned char smem_gen[];
+  unsigned char *smem_raw = smem_gen;
+  float *vec = reinterpret_cast<float *>(smem_raw);
+  __shared__ int s_count;
+  const int P = c.padded, dim = c.dim;
+  const int item = blockIdx.x;
+  const int h = head0 + item / nq;
+  const int tid = threadIdx.x;
+  const float *w = sorted_w + (size_t)item * w_stride;
+  const int *tok = sorted_tok + (size_t)item * w_stride;
+  if (tid == 0) {
+    float mass = 0.f;
+    int ii = 0;
+    for (; ii + 3 < n && mass < c.v_mass; ii += 4)
+      mass = __fadd_rn(mass, __fadd_rn(__fadd_rn(__fadd_rn(w[ii], w[ii + 1]), w[ii + 2]), w[ii + 3]));
+    for (; ii < n && mass < c.v_mass; ++ii) mass = __fadd_rn(mass, w[ii]);
+    s_count = ii;
+  }
+  __syncthreads();
+  const int count = s_count;
+  const uint8_t *vbase = c.v_slab + (size_t)h * c.v_stride;
+  const float *vsc = c.v_scale + (size_t)h * c.s_stride;
+  const float *vcb = c_cb[c.v_bits - 2];
+  const float isp = 1.f / sqrtf((float)P);
+  for (int j = tid; j < P; j += CG_THREADS) {
+    float av = 0.f;
+    for (int i = 0; i < count; ++i) {
+      const int s = tok[i];
+      av += (w[i] * vsc[s] * isp) * vcb[unpack_at(vbase + (size_t)s * c.v_row, j, c.v_bits)];
+    }
+    vec[j] = av;
+  }
+  __syncthreads();
+  block_butterflies(vec, P);
+  const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
+  float *o = out + (size_t)item * dim;
+  for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
+}
+
+} // namespace aq

@@ -1,0 +1,405 @@
+// Streaming split-KV decode-attention kernel for the bandwidth-bound shapes
+// (2- or 4-bit K and V, padded dimension 64 or 128, dense V).
+//
+// Replaces the same upstream code as compute_general.cuh -- the quantised
+// branch of AttentionHead::compute (attention/attention.cpp:526-563, :606-633)
+// with compute_avx2 (:373-474) and fwht_inverse (core/fwht.cpp:106-134) -- but
+// organised for HBM streaming on sm_100a:
+//
+//  * persistent blocks, one per SM; a work item is (head, query, KV span);
+//  * a producer warp feeds a ring of 8 KB shared-memory stages with bulk
+//    (TMA) copies, first the span's K rows, then its V rows -- K and V are
+//    separate slabs and are read as separate streams; the producer runs ahead
+//    across phase and item boundaries so HBM never waits for arithmetic;
+//  * K scoring never unpacks an index: a table T[byte][column] =
+//    sum over the 2 (4-bit) or 4 (2-bit) coordinates packed in that byte of
+//    q_rot[coord]*centroid is built once per item; a score is the sum of one
+//    table entry per packed byte.  Lanes own byte columns so every table read
+//    is bank-conflict free, and the table sits on a 64 KB boundary so a
+//    single byte-permute forms the address;
+//  * the softmax is exact two-pass over the span (max, then exp), like
+//    upstream, with the scores held in shared memory;
+//  * V accumulation is the dual trick: instead of decoding V, the weight of a
+//    token is added into bucket[byte][column]; after the span, each output
+//    coordinate is the centroid-weighted sum of its column's 256 buckets.
+//    That costs one shared-memory reduction per packed byte (4 coordinates at
+//    2 bits) instead of one multiply-add per coordinate;
+//  * one inverse Walsh-Hadamard transform at the end (or in the merge kernel
+//    when the sequence is split).
+//
+// No tensor cores: the path is ~5 FLOP/byte of irregular table work.
+#pragma once
+#include "common.cuh"
+
+namespace aq {
+
+constexpr int CS_CONSUMERS = 256;           // 8 consumer warps
+constexpr int CS_THREADS = CS_CONSUMERS + 32; // + 1 producer warp
+constexpr int CS_STAGE_BYTES = 8192;
+constexpr int CS_STAGES = 6;
+constexpr int CS_SPAN_MAX = 8192;           // tokens per work item (scores kept in shared memory)
+constexpr int CS_TABLE_BYTES = 65536;       // [256][64] floats
+constexpr size_t CS_SMEM_BYTES = 65536 /* alignment slack, holds the ring */ + CS_TABLE_BYTES /* K table */ +
+                                 CS_TABLE_BYTES /* V buckets */ + CS_SPAN_MAX * 4 /* scores */ + 2048 /* misc */;
+
+struct StreamLaunch {
+  CacheView c;
+  const float *q; // [heads_in_call][nq][dim]
+  float *out;     // [heads_in_call][nq][dim]                 (n_splits == 1)
+  float *partial; // [n_splits][heads_in_call*nq][2+P]        (n_splits  > 1)
+  int head0, heads_in_call, nq;
+  int n, n_splits, span; // span: tokens per split, multiple of 256
+  int force_partial;     // write the partial even when there is a single span
+  int *status;
+};
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CS_CONSUMERS) : "memory"); }
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void red_shared_add(uint32_t addr, float v) {
+  asm volatile("red.shared.add.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ float consumer_reduce(float v, float *red, bool is_max) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = is_max ? warp_max(v) : warp_sum(v);
+  consumer_sync();
+  if (lane == 0) red[warp] = v;
+  consumer_sync();
+  float r = red[0];
+#pragma unroll
+  for (int i = 1; i < CS_CONSUMERS / 32; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+  return r;
+}
+
+__device__ __forceinline__ void consumer_butterflies(float *x, int p) {
+  for (int len = 1; len < p; len <<= 1) {
+    for (int t = threadIdx.x; t < (p >> 1); t += CS_CONSUMERS) {
+      int i = ((t / len) * (len << 1)) + (t % len);
+      float a = x[i], b = x[i + len];
+      x[i] = a + b;
+      x[i + len] = a - b;
+    }
+    consumer_sync();
+  }
+}
+
+// Sum STEPS per-lane partials across the 8 lanes of a token group so that
+// each lane ends with complete sums; returns the value this lane owns and the
+// step it belongs to (8 steps: lane wl owns step wl; 4 steps: lanes wl, wl^1
+// own step wl>>1).
+template <int STEPS>
+__device__ __forceinline__ float group_transpose_sum(float (&v)[STEPS], int wl) {
+  static_assert(STEPS == 4 || STEPS == 8, "4 or 8 steps");
+  int cnt = STEPS;
+#pragma unroll
+  for (int off = 4; off >= 1; off >>= 1) {
+    if (cnt > 1) {
+      const int half = cnt >> 1;
+      const bool up = (wl & off) != 0;
+#pragma unroll
+      for (int i = 0; i < STEPS / 2; ++i) {
+        if (i < half) {
+          float keep = up ? v[i + half] : v[i];
+          float send = up ? v[i] : v[i + half];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+      }
+      cnt = half;
+    } else {
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+    }
+  }
+  return v[0];
+}
+
+// KB/VB: bits; KW/VW: 32-bit words per packed row (8 or 16).
+template <int KB, int KW, int VB, int VW>
+__global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const StreamLaunch a) {
+  constexpr int P = KW * 32 / KB;
+  static_assert(P == VW * 32 / VB, "K and V rows must describe the same padded dimension");
+  constexpr int KROW = KW * 4, VROW = VW * 4;
+  constexpr int TKN = CS_STAGE_BYTES / KROW, TVN = CS_STAGE_BYTES / VROW; // tokens per stage
+  constexpr int KSTEPS = TKN / 8 / 4, VSTEPS = TVN / 8 / 4;                 // 4 tokens per warp step
+  constexpr int KWPL = KW / 8, VWPL = VW / 8;                               // words per lane
+  constexpr int KC = KW * 4, VC = VW * 4;                                   // byte columns
+  constexpr int KE = 8 / KB, VE = 8 / VB;                                   // coordinates per byte
+  constexpr int RING_BYTES = CS_STAGES * CS_STAGE_BYTES;
+
+  extern __shared__ __align__(1024) unsigned char smem_stream[];
+  unsigned char *smem = smem_stream;
+  const uint32_t base = smem_u32(smem);
+  const uint32_t table_addr = (base + 65535u) & ~65535u; // 64 KB aligned: low 16 address bits are free
+  const uint32_t front = table_addr - base;
+  unsigned char *table_p = smem + front;
+  const uint32_t bucket_addr = table_addr + CS_TABLE_BYTES;
+  float *bucket = reinterpret_cast<float *>(table_p + CS_TABLE_BYTES);
+  float *sc = bucket + CS_TABLE_BYTES / 4;
+  unsigned char *misc = reinterpret_cast<unsigned char *>(sc + CS_SPAN_MAX);
+  float *qr = reinterpret_cast<float *>(misc);          // P floats (<= 512 B)
+  float *red = qr + 128;                                 // 64 floats
+  uint64_t *full = reinterpret_cast<uint64_t *>(red + 64);
+  uint64_t *empty = full + CS_STAGES;
+  int *s_fail = reinterpret_cast<int *>(empty + CS_STAGES);
+  unsigned char *ring = (front >= (uint32_t)RING_BYTES) ? smem : (misc + 2048);
+  const bool layout_ok = front >= (uint32_t)RING_BYTES || (65536u - front) >= (uint32_t)RING_BYTES + 0u;
+
+  const int tid = threadIdx.x;
+  const CacheView &c = a.c;
+  const int dim = c.dim;
+  const int items_base = a.heads_in_call * a.nq;
+  const int n_items = items_base * a.n_splits;
+
+  if (tid == 0) {
+    for (int s = 0; s < CS_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], CS_CONSUMERS / 32);
+    }
+    *s_fail = layout_ok ? 0 : 2;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (!layout_ok) {
+    if (tid == 0) atomicExch(a.status, 2);
+    return;
+  }
+
+  // ======================= producer warp ====================================
+  if (tid >= CS_CONSUMERS) {
+    if (tid != CS_CONSUMERS) return;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const int split = item % a.n_splits, hq = item / a.n_splits;
+      const int h = a.head0 + hq / a.nq;
+      const int t0 = min(a.n, split * a.span), t1 = min(a.n, t0 + a.span);
+      const uint8_t *kb = c.k_slab + (size_t)h * c.k_stride;
+      const uint8_t *vb = c.v_slab + (size_t)h * c.v_stride;
+      for (int pass = 0; pass < 2; ++pass) {
+        const int rowb = pass ? VROW : KROW, tn = pass ? TVN : TKN;
+        const uint8_t *src = pass ? vb : kb;
+        for (int t = t0; t < t1; t += tn) {
+          if (*reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(&empty[stage], phase ^ 1u)) {
+            *reinterpret_cast<volatile int *>(s_fail) = 1;
+            atomicExch(a.status, 1);
+          }
+          const uint32_t bytes = ((uint32_t)(min(tn, t1 - t) * rowb) + 15u) & ~15u;
+          mbar_expect_tx(&full[stage], bytes);
+          bulk_g2s(ring + (size_t)stage * CS_STAGE_BYTES, src + (size_t)t * rowb, bytes, &full[stage]);
+          if (++stage == CS_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    return;
+  }
+
+  // ======================= consumer warps ===================================
+  const int lane = tid & 31, warp = tid >> 5;
+  const int tq = lane >> 3, wl = lane & 7;
+  // Per-lane constants.  The lane reads word kword[m] of its token's row and
+  // visits that word's four bytes in the rotated order (k + tq) & 3, which puts
+  // the 32 lanes of a warp on 32 different banks of the table / bucket arrays.
+  int kword[KWPL], vword[VWPL];
+  uint32_t ksel[4], kconst[KWPL][4], vconst[VWPL][4];
+#pragma unroll
+  for (int m = 0; m < KWPL; ++m) kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+#pragma unroll
+  for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+  // V buckets: with 32 byte columns the array has room for two copies; warps
+  // 4..7 use the second one (columns 32..63) to halve collisions.
+  const int vcol_off = (VC == 32 && warp >= 4) ? 32 : 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int kk = (k + tq) & 3;
+    ksel[k] = 0x7604u | ((uint32_t)kk << 4); // result = {const.b0, data.byte[kk], const.b2, const.b3}
+#pragma unroll
+    for (int m = 0; m < KWPL; ++m) kconst[m][k] = table_addr | (uint32_t)((4 * kword[m] + kk) << 2);
+#pragma unroll
+    for (int m = 0; m < VWPL; ++m) vconst[m][k] = bucket_addr | (uint32_t)((4 * vword[m] + kk + vcol_off) << 2);
+  }
+  float *table = reinterpret_cast<float *>(table_p);
+  const float *kcb = c_cb[KB - 2], *vcb = c_cb[VB - 2];
+  const float isp = 1.f / sqrtf((float)P);
+  const float attn_s = 1.f / (sqrtf((float)dim) * (float)P);
+
+  int stage = 0;
+  uint32_t phase = 0;
+  auto wait_full = [&]() {
+    if (*reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(&full[stage], phase)) {
+      *reinterpret_cast<volatile int *>(s_fail) = 1;
+      atomicExch(a.status, 1);
+    }
+  };
+  auto release = [&]() {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[stage]);
+    if (++stage == CS_STAGES) { stage = 0; phase ^= 1u; }
+  };
+
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int split = item % a.n_splits, hq = item / a.n_splits;
+    const int hl = hq / a.nq;
+    const int h = a.head0 + hl;
+    const int t0 = min(a.n, split * a.span), t1 = min(a.n, t0 + a.span);
+    const int len = t1 - t0;
+    const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
+    const float *q = a.q + (size_t)hq * dim;
+
+    // ---- rotate the query (attention.cpp:537-550) -------------------------
+    if (tid < P) qr[tid] = tid < dim ? q[tid] : 0.f;
+    consumer_sync();
+    float part = (tid < dim) ? qr[tid] * qr[tid] : 0.f;
+    const float qn = sqrtf(consumer_reduce(part, red, false) + 1e-12f);
+    if (tid < P) qr[tid] = qr[tid] * (1.f / qn) * sign_of(sg, tid);
+    consumer_sync();
+    consumer_butterflies(qr, P);
+    if (tid < P) qr[tid] = qr[tid] * isp * (sqrtf((float)P) * qn);
+    // ---- zero the buckets, build the K byte table ---------------------------
+    for (int i = tid; i < CS_TABLE_BYTES / 4; i += CS_CONSUMERS) bucket[i] = 0.f;
+    consumer_sync();
+    {
+      // thread -> column (consecutive lanes, consecutive banks), a quarter of the byte values
+      const int col = tid & 63, bq = tid >> 6;
+      if (col < KC) {
+        if (KE == 2) {
+          float lo[16];
+          const float q0 = qr[2 * col], q1 = qr[2 * col + 1];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) lo[i] = q1 * kcb[i];
+#pragma unroll
+          for (int hi = 0; hi < 4; ++hi) {
+            const int hv = bq * 4 + hi;
+            const float av = q0 * kcb[hv];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) table[(hv * 16 + i) * 64 + col] = av + lo[i];
+          }
+        } else { // 4 two-bit coordinates per byte, first coordinate in the top bits
+          float t23[16];
+          const float q0 = qr[4 * col], q1 = qr[4 * col + 1], q2 = qr[4 * col + 2], q3 = qr[4 * col + 3];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) t23[i] = q2 * kcb[i >> 2] + q3 * kcb[i & 3];
+#pragma unroll
+          for (int hi = 0; hi < 4; ++hi) {
+            const int hv = bq * 4 + hi;
+            const float t01 = q0 * kcb[hv >> 2] + q1 * kcb[hv & 3];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) table[(hv * 16 + i) * 64 + col] = t01 + t23[i];
+          }
+        }
+      }
+    }
+    consumer_sync();
+
+    // ---- K stream: raw dot products into sc[] ---------------------------------------
+    for (int t = t0; t < t1; t += TKN) {
+      wait_full();
+      const uint32_t st_addr = smem_u32(ring + (size_t)stage * CS_STAGE_BYTES);
+      float pv[KSTEPS];
+#pragma unroll
+      for (int s = 0; s < KSTEPS; ++s) {
+        const int tok = warp * (TKN / 8) + 4 * s + tq; // token within the stage
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int m = 0; m < KWPL; ++m) {
+          uint32_t d;
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(d) : "r"(st_addr + tok * KROW + kword[m] * 4));
+          a0 += lds_f32(__byte_perm(d, kconst[m][0], ksel[0]));
+          a1 += lds_f32(__byte_perm(d, kconst[m][1], ksel[1]));
+          a0 += lds_f32(__byte_perm(d, kconst[m][2], ksel[2]));
+          a1 += lds_f32(__byte_perm(d, kconst[m][3], ksel[3]));
+        }
+        pv[s] = a0 + a1;
+      }
+      const float total = group_transpose_sum<KSTEPS>(pv, wl);
+      const int step = KSTEPS == 8 ? wl : (wl >> 1);
+      const int tok = warp * (TKN / 8) + 4 * step + tq;
+      if ((KSTEPS == 8 || (wl & 1) == 0) && t + tok < t1) sc[t - t0 + tok] = total;
+      release();
+    }
+    consumer_sync();
+
+    // ---- exact two-pass softmax over the span ------------------------------------------
+    const float *ksc = c.k_scale + (size_t)h * c.s_stride + t0;
+    const float *vsc = c.v_scale + (size_t)h * c.s_stride + t0;
+    float mx = -INFINITY;
+    for (int i = tid; i < len; i += CS_CONSUMERS) {
+      const float s = sc[i] * attn_s * ksc[i];
+      sc[i] = s;
+      mx = fmaxf(mx, s);
+    }
+    mx = consumer_reduce(mx, red, true);
+    float ls = 0.f;
+    const int len_pad = min(CS_SPAN_MAX, (len + TVN - 1) / TVN * TVN);
+    for (int i = tid; i < len_pad; i += CS_CONSUMERS) {
+      float w = 0.f;
+      if (i < len) {
+        const float e = expf(sc[i] - mx);
+        ls += e;
+        w = e * vsc[i] * isp;
+      }
+      sc[i] = w;
+    }
+    ls = consumer_reduce(ls, red, false);
+
+    // ---- V stream: add each token's weight into bucket[byte][column] ---------------------
+    for (int t = t0; t < t1; t += TVN) {
+      wait_full();
+      const uint32_t st_addr = smem_u32(ring + (size_t)stage * CS_STAGE_BYTES);
+#pragma unroll
+      for (int s = 0; s < VSTEPS; ++s) {
+        const int tok = warp * (TVN / 8) + 4 * s + tq;
+        const float w = sc[t - t0 + tok];
+#pragma unroll
+        for (int m = 0; m < VWPL; ++m) {
+          uint32_t d;
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(d) : "r"(st_addr + tok * VROW + vword[m] * 4));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) red_shared_add(__byte_perm(d, vconst[m][k], ksel[k]), w);
+        }
+      }
+      release();
+    }
+    consumer_sync();
+
+    // ---- buckets -> rotated-domain accumulator -------------------------------------------
+    // acc[j] = sum over byte values of bucket[byte][column(j)] * centroid[digit_j(byte)]
+    {
+      constexpr int PARTS = CS_CONSUMERS / P; // 2 (P=128) or 4 (P=64)
+      const int j = tid % P, part = tid / P;
+      const int col = j / VE, e = j % VE;
+      const int shift = 8 - VB * (e + 1);
+      float av = 0.f;
+      for (int b = part; b < 256; b += PARTS) {
+        float bv = bucket[b * 64 + col];
+        if (VC == 32) bv += bucket[b * 64 + 32 + col];
+        av += bv * vcb[(b >> shift) & ((1 << VB) - 1)];
+      }
+      consumer_sync(); // all bucket reads done before sc[] is reused as fold space
+      sc[tid] = av;
+      consumer_sync();
+      if (tid < P) {
+        float s = 0.f;
+#pragma unroll
+        for (int g = 0; g < PARTS; ++g) s += sc[g * P + tid];
+        qr[tid] = s; // qr is free now
+      }
+      consumer_sync();
+    }
+    if (a.n_splits > 1 || a.force_partial) {
+      float *pp = a.partial + ((size_t)split * items_base + hq) * (size_t)(2 + P);
+      if (tid == 0) { pp[0] = mx; pp[1] = ls; }
+      if (tid < P) pp[2 + tid] = qr[tid];
+    } else {
+      if (tid < P) qr[tid] *= (1.f / ls);
+      consumer_sync();
+      consumer_butterflies(qr, P);
+      if (tid < dim) a.out[(size_t)hq * dim + tid] = qr[tid] * isp * sign_of(sg, tid);
+    }
+    consumer_sync();
+  }
+}
+
+} // namespace aq

@@ -1,0 +1,201 @@
+"""MHAContext: the class upstream exposes from its pybind11 module ``adaptq_py``
+(adapters/adapter_python.cpp:30-93), here over the CUDA library's C ABI, plus
+the all-heads calls of include/adaptq_b200.h.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+
+try:  # torch is only needed for device-tensor arguments
+    import torch
+except Exception:  # pragma: no cover
+    torch = None
+
+
+def _as_arg(x, shape_check=None):
+    """Return (pointer, keepalive, is_device).  Accepts numpy arrays (host) and
+    torch tensors (host or CUDA); both must be float32 and contiguous."""
+    if torch is not None and isinstance(x, torch.Tensor):
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            x = x.detach().to(torch.float32).contiguous()
+        return C.c_void_p(x.data_ptr()), x, x.is_cuda
+    a = np.ascontiguousarray(x, dtype=np.float32)
+    return C.c_void_p(a.ctypes.data), a, False
+
+
+class MHAContext:
+    """n_heads independent quantized KV caches on the current CUDA device.
+
+    Same constructor keywords, methods and error behaviour as upstream's
+    ``adaptq_py.MHAContext``; ``append_all`` / ``compute_all`` are additions.
+    """
+
+    def __init__(self, n_heads, head_dim, k_bits, v_bits, capacity, seed=0, v_mass=0.95,
+                 hybrid_thresh=512, seeds=None):
+        L = _lib.load()
+        self._L = L
+        self._h = None
+        if seeds is not None:
+            arr = (C.c_uint64 * len(seeds))(*[int(s) & (2**64 - 1) for s in seeds])
+            if len(seeds) != n_heads:
+                raise ValueError("len(seeds) must equal n_heads")
+            h = L.adaptq_mha_create_seeded(n_heads, arr, head_dim, k_bits, v_bits, capacity,
+                                           C.c_float(v_mass), hybrid_thresh)
+        else:
+            h = L.adaptq_mha_create(n_heads, head_dim, k_bits, v_bits, capacity,
+                                    C.c_uint64(int(seed) & (2**64 - 1)), C.c_float(v_mass), hybrid_thresh)
+        if not h:
+            raise RuntimeError(_lib.last_error() or "adaptq_mha_create failed")
+        self._h = C.c_void_p(h)
+        self._n_heads = n_heads
+        self._head_dim = head_dim
+        info = _lib.MhaInfo()
+        L.adaptq_mha_info(self._h, C.byref(info))
+        self.info = info
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.adaptq_mha_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- upstream surface -----------------------------------------------------
+    def append(self, head, key, val, pos):
+        k = np.ascontiguousarray(key, dtype=np.float32)
+        v = np.ascontiguousarray(val, dtype=np.float32)
+        if k.ndim != 1 or v.ndim != 1 or k.shape[0] != self._head_dim or v.shape[0] != self._head_dim:
+            raise ValueError("key/val dim mismatch")
+        self._L.adaptq_mha_append(self._h, head, k.ctypes.data, v.ctypes.data, pos)
+        self._raise_if_error()
+
+    def compute(self, head, query):
+        q = np.ascontiguousarray(query, dtype=np.float32)
+        if q.ndim != 1 or q.shape[0] != self._head_dim:
+            raise ValueError("query dim mismatch")
+        out = np.empty(self._head_dim, dtype=np.float32)
+        n = self._L.adaptq_mha_compute(self._h, head, q.ctypes.data, out.ctypes.data)
+        if n < 0:
+            raise RuntimeError(_lib.last_error())
+        return out
+
+    def compute_batch(self, head, queries):
+        q = np.ascontiguousarray(queries, dtype=np.float32)
+        if q.ndim != 2 or q.shape[1] != self._head_dim:
+            raise ValueError("queries dim mismatch")
+        out = np.empty_like(q)
+        n = self._L.adaptq_mha_compute_batch(self._h, head, q.ctypes.data, q.shape[0], out.ctypes.data)
+        if n < 0:
+            raise RuntimeError(_lib.last_error())
+        return out
+
+    def reset(self):
+        self._L.adaptq_mha_reset(self._h)
+
+    def kv_bytes(self):
+        return int(self._L.adaptq_mha_total_kv_bytes(self._h))
+
+    @property
+    def n_heads(self):
+        return self._n_heads
+
+    @property
+    def head_dim(self):
+        return self._head_dim
+
+    # -- all heads at once (include/adaptq_b200.h) -------------------------------
+    def append_all(self, keys, vals, pos0=0):
+        """keys, vals: [n_tokens, n_heads, dim] (or [n_heads, dim] for one token);
+        numpy (host) or torch (host / CUDA) float32."""
+        kp, kk, _ = _as_arg(keys)
+        vp, vk, _ = _as_arg(vals)
+        shape = tuple(kk.shape)
+        if len(shape) == 2:
+            shape = (1,) + shape
+        if len(shape) != 3 or shape[1] != self._n_heads or shape[2] != self._head_dim or tuple(vk.shape)[-2:] != shape[-2:]:
+            raise ValueError(f"keys and vals must be shape (T, {self._n_heads}, {self._head_dim})")
+        rc = self._L.adaptq_mha_append_batch(self._h, kp, vp, shape[0], pos0)
+        if rc != 0:
+            raise RuntimeError(_lib.last_error())
+
+    def compute_all(self, queries, out=None):
+        """queries: [n_heads, dim] or [n_heads, nq, dim].  Returns an array/tensor of
+        the same shape, on the same device as `queries`."""
+        qp, qk, is_dev = _as_arg(queries)
+        shape = tuple(qk.shape)
+        nq = 1 if len(shape) == 2 else shape[1]
+        if shape[0] != self._n_heads or shape[-1] != self._head_dim or len(shape) not in (2, 3):
+            raise ValueError(f"queries must be shape ({self._n_heads}, [nq,] {self._head_dim})")
+        if out is None:
+            out = torch.empty_like(qk) if (torch is not None and isinstance(qk, torch.Tensor)) else np.empty_like(qk)
+        op, ok, _ = _as_arg(out)
+        n = self._L.adaptq_mha_compute_all(self._h, qp, nq, op)
+        if n < 0:
+            raise RuntimeError(_lib.last_error())
+        return ok
+
+    def compute_partial(self, queries, out=None):
+        """Un-normalised split-KV partials [n_heads, nq, 2+padded] for sequence sharding."""
+        qp, qk, _ = _as_arg(queries)
+        shape = tuple(qk.shape)
+        nq = 1 if len(shape) == 2 else shape[1]
+        pf = self._L.adaptq_mha_partial_floats(self._h)
+        if out is None:
+            if torch is not None and isinstance(qk, torch.Tensor):
+                out = torch.empty((self._n_heads, nq, pf), dtype=torch.float32, device=qk.device)
+            else:
+                out = np.empty((self._n_heads, nq, pf), dtype=np.float32)
+        op, ok, _ = _as_arg(out)
+        if self._L.adaptq_mha_compute_partial(self._h, qp, nq, op) < 0:
+            raise RuntimeError(_lib.last_error())
+        return ok
+
+    def merge_partials(self, partials, nq=1, out=None):
+        """partials: [n_parts, n_heads, nq, 2+padded] -> [n_heads, nq, dim]."""
+        pp, pk, _ = _as_arg(partials)
+        n_parts = pk.shape[0]
+        if out is None:
+            if torch is not None and isinstance(pk, torch.Tensor):
+                out = torch.empty((self._n_heads, nq, self._head_dim), dtype=torch.float32, device=pk.device)
+            else:
+                out = np.empty((self._n_heads, nq, self._head_dim), dtype=np.float32)
+        op, ok, _ = _as_arg(out)
+        if self._L.adaptq_mha_merge_partials(self._h, pp, n_parts, nq, op) < 0:
+            raise RuntimeError(_lib.last_error())
+        return ok
+
+    def set_stream(self, cuda_stream_ptr):
+        self._L.adaptq_mha_set_stream(self._h, C.c_void_p(cuda_stream_ptr))
+
+    def synchronize(self):
+        if self._L.adaptq_mha_synchronize(self._h) != 0:
+            raise RuntimeError(_lib.last_error())
+
+    def export_head(self, head):
+        """Host copy of one head's cache in upstream's layout (for parity checks)."""
+        i = self.info
+        k = np.zeros((i.capacity, i.k_row_bytes), dtype=np.uint8)
+        v = np.zeros((i.capacity, i.v_row_bytes), dtype=np.uint8)
+        ks = np.zeros(i.capacity, dtype=np.float32)
+        vs = np.zeros(i.capacity, dtype=np.float32)
+        sg = np.zeros(i.padded, dtype=np.int8)
+        rh, rs, mt = C.c_int(0), C.c_int(0), C.c_int(0)
+        rc = self._L.adaptq_mha_export_head(self._h, head, k.ctypes.data, v.ctypes.data, ks.ctypes.data,
+                                            vs.ctypes.data, sg.ctypes.data, C.byref(rh), C.byref(rs), C.byref(mt))
+        if rc != 0:
+            raise RuntimeError(_lib.last_error())
+        return {"k_rows": k, "v_rows": v, "k_scale": ks, "v_scale": vs, "signs": sg,
+                "ring_head": rh.value, "ring_size": rs.value, "mirror_tokens": mt.value}
+
+    def _raise_if_error(self):
+        e = _lib.last_error()
+        if e:
+            raise RuntimeError(e)

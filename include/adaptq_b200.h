@@ -1,0 +1,99 @@
+/*
+ * adaptq_b200.h -- batched entry points of the B200 AdapTQ engine.
+ *
+ * The upstream interface (adaptq.h) moves one float[dim] vector of one head
+ * per call; upstream's own callers loop over heads in Python
+ * (adaptq/core.py:53-57, :70-72).  That shape cannot keep a GPU busy, so the
+ * same two operations are also offered over ALL heads of a handle at once.
+ * They are additions: upstream has no counterpart, and they compute exactly
+ * what a loop over adaptq_mha_append / adaptq_mha_compute(_batch) computes.
+ *
+ * Pointers may be host or device memory (the library asks the CUDA runtime
+ * which); device pointers are used in place, host pointers are staged.
+ * All functions return -1 and set adaptq_last_error() on failure.
+ */
+#ifndef ADAPTQ_B200_EXT_H
+#define ADAPTQ_B200_EXT_H
+
+#include "adaptq.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Like adaptq_mha_create (upstream core/adaptq_c_api.cpp:149-165) but every
+ * head-instance gets its own seed, so one handle can hold the heads of many
+ * layers and sequences (upstream builds one Engine per layer with seed
+ * 42 ^ layer and lets the handle derive head seeds from it). */
+adaptq_mha_t adaptq_mha_create_seeded(int n_heads, const uint64_t *seeds,
+                                      int dim, int k_bits, int v_bits,
+                                      int capacity, float v_mass,
+                                      int hybrid_thresh);
+
+/* Append n_tokens tokens to every head.  keys, vals: float
+ * [n_tokens][n_heads][dim].  Equals, for t in order and every head h,
+ * adaptq_mha_append(mha, h, keys[t][h], vals[t][h], token_pos0 + t)
+ * (upstream attention/attention.cpp:338-366).  Returns 0. */
+int adaptq_mha_append_batch(adaptq_mha_t mha, const float *keys,
+                            const float *vals, int n_tokens, int token_pos0);
+
+/* Attention for every head, queries_per_head queries each.  queries, outs:
+ * float [n_heads][queries_per_head][dim].  Equals adaptq_mha_compute_batch
+ * on every head (upstream attention/attention.cpp:480-677); the cache is
+ * read once per head.  Returns the largest per-head token count. */
+int adaptq_mha_compute_all(adaptq_mha_t mha, const float *queries,
+                           int queries_per_head, float *outs);
+
+/* Sequence sharding.  When the tokens of ONE logical cache are spread over
+ * several handles (for instance token t on GPU t mod G), each handle
+ * produces un-normalised softmax partials in the rotated domain:
+ *   partials: float [n_heads][queries_per_head][adaptq_mha_partial_floats()]
+ *   = { running max m, sum l = sum_i exp(logit_i - m), acc[padded] }.
+ * adaptq_mha_merge_partials combines n_parts of them (laid out
+ * [n_parts][n_heads][queries_per_head][...]; gathered by the caller, e.g.
+ * with an NCCL all-gather), applies the single inverse transform and
+ * writes outs [n_heads][queries_per_head][dim].  Dense V and quantized K
+ * only (v_mass <= 0, hybrid_thresh == 0, k_bits != 16, v_bits != 16). */
+int adaptq_mha_partial_floats(adaptq_mha_t mha);
+int adaptq_mha_compute_partial(adaptq_mha_t mha, const float *queries,
+                               int queries_per_head, float *partials);
+int adaptq_mha_merge_partials(adaptq_mha_t mha, const float *partials,
+                              int n_parts, int queries_per_head, float *outs);
+
+/* Use `cuda_stream` (a cudaStream_t; NULL = the default stream) for all
+ * further work of this handle. */
+int adaptq_mha_set_stream(adaptq_mha_t mha, void *cuda_stream);
+/* Wait until everything queued on the handle's stream has finished; returns
+ * -1 and sets the error string if a kernel reported a fault. */
+int adaptq_mha_synchronize(adaptq_mha_t mha);
+
+typedef struct {
+  int n_heads, dim, padded, k_bits, v_bits, capacity, hybrid_thresh;
+  int k_row_bytes, v_row_bytes; /* as upstream cache/ring_buffer.cpp:52-53 */
+  int device;                   /* CUDA device ordinal holding the cache */
+  float v_mass;
+  size_t device_bytes;          /* GPU memory owned by the handle */
+} adaptq_mha_info_t;
+int adaptq_mha_info(adaptq_mha_t mha, adaptq_mha_info_t *info);
+
+/* Copy one head's cache to HOST buffers in upstream's memory layout
+ * (include/ring_buffer.h:61-66): k_rows capacity*k_row_bytes bytes, v_rows
+ * capacity*v_row_bytes bytes, k_scale/v_scale capacity floats, signs
+ * `padded` int8 (+1/-1).  Any output pointer may be NULL.  ring_head /
+ * ring_size / mirror_tokens receive the ring state. */
+int adaptq_mha_export_head(adaptq_mha_t mha, int head_idx, uint8_t *k_rows,
+                           uint8_t *v_rows, float *k_scale, float *v_scale,
+                           int8_t *signs, int *ring_head, int *ring_size,
+                           int *mirror_tokens);
+
+/* Number of CUDA kernels this library has launched in this process. */
+unsigned long long adaptq_kernel_launches(void);
+
+/* Force a code path, for tests: 0 = automatic, 1 = general-purpose kernels
+ * only, 2 = refuse shapes the specialised kernels do not cover. */
+int adaptq_set_kernel_policy(int policy);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADAPTQ_B200_EXT_H */

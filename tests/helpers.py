@@ -1,0 +1,95 @@
+"""Shared helpers for the parity tests: seeded inputs, CPU-checker runs, tolerances."""
+from __future__ import annotations
+
+import numpy as np
+
+from oracle import loader
+
+# Tolerance for attention outputs and scales (fp32): |a-b| <= ATOL + RTOL*|b|
+RTOL = 1e-5
+ATOL = 1e-4
+
+
+def make_kv(rng, n_tokens, heads, dim, dist="normal"):
+    """[n_tokens, heads, dim] float32 keys and values."""
+    shape = (n_tokens, heads, dim)
+    if dist == "normal":
+        k, v = rng.standard_normal(shape), rng.standard_normal(shape)
+    elif dist == "student3":
+        k, v = rng.standard_t(3, shape), rng.standard_t(3, shape)
+    elif dist == "student4_outlier":  # heavy tails + 3 fixed channels per head scaled x10
+        k, v = rng.standard_t(4, shape), rng.standard_t(4, shape)
+        ch = np.random.default_rng(1).choice(dim, size=(heads, 3))
+        for h in range(heads):
+            k[:, h, ch[h]] *= 10.0
+            v[:, h, ch[h]] *= 10.0
+    elif dist == "normal_outlier":  # 1% of entries replaced by N(0,20)
+        k, v = rng.standard_normal(shape), rng.standard_normal(shape)
+        for a in (k, v):
+            m = rng.random(shape) < 0.01
+            a[m] = rng.standard_normal(int(m.sum())) * 20.0
+    elif dist == "lognormal_channel":  # N(0,1) x per-channel log-normal(0, 0.5) scale
+        s = np.exp(0.5 * rng.standard_normal((1, heads, dim)))
+        k, v = rng.standard_normal(shape) * s, rng.standard_normal(shape) * s
+    elif dist == "tiny":
+        k, v = rng.standard_normal(shape) * 1e-7, rng.standard_normal(shape) * 3e-7
+    else:
+        raise ValueError(dist)
+    return k.astype(np.float32), v.astype(np.float32)
+
+
+class CpuHeads:
+    """`heads` independent CPU-checker heads seeded like a multi-head handle."""
+
+    def __init__(self, lib, heads, dim, k_bits, v_bits, capacity, base_seed, v_mass=0.0, hybrid_thresh=0, seeds=None):
+        self.heads = [loader.Head(lib, dim, k_bits, v_bits, capacity,
+                                  seeds[h] if seeds is not None else loader.mha_head_seed(base_seed, h),
+                                  v_mass, hybrid_thresh) for h in range(heads)]
+        self.dim = dim
+
+    def append_many(self, keys, vals):  # [T, H, dim]
+        for h, hd in enumerate(self.heads):
+            hd.append_many(keys[:, h, :], vals[:, h, :])
+
+    def compute(self, q):  # [H, dim] -> [H, dim]
+        return np.stack([hd.compute(q[h])[0] for h, hd in enumerate(self.heads)])
+
+    def compute_batch(self, q):  # [H, nq, dim]
+        return np.stack([hd.compute_batch(q[h])[0] for h, hd in enumerate(self.heads)])
+
+    def reset(self):
+        for hd in self.heads:
+            hd.reset()
+
+
+def assert_close(got, want, what="", rtol=RTOL, atol=ATOL):
+    got = np.asarray(got, dtype=np.float32)
+    want = np.asarray(want, dtype=np.float32)
+    assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    bound = atol + rtol * np.abs(want.astype(np.float64))
+    bad = err > bound
+    if bad.any():
+        i = np.unravel_index(np.argmax(err - bound), err.shape)
+        raise AssertionError(f"{what}: {int(bad.sum())} of {bad.size} outside tolerance; worst at {i}: "
+                             f"got {got[i]!r} want {want[i]!r} (|err| {err[i]:.3e}, bound {bound[i]:.3e})")
+
+
+def assert_cache_equal(exported, head: loader.Head, what=""):
+    """Packed rows bit-exact, scales bit-exact, ring state equal (live slots only)."""
+    n, cap = head.size, head.capacity
+    assert exported["ring_size"] == n, f"{what}: ring size {exported['ring_size']} vs {n}"
+    assert exported["ring_head"] == head.ring_head, f"{what}: ring head"
+    assert exported["mirror_tokens"] == head.mirror_tokens, f"{what}: mirror tokens"
+    live = np.arange(cap) if n == cap else np.arange(n)
+    kd, vd = head.k_data(), head.v_data()
+    ke, ve = exported["k_rows"], exported["v_rows"]
+    assert ke.shape == kd.shape and ve.shape == vd.shape, f"{what}: row geometry"
+    bad_k = np.nonzero((ke[live] != kd[live]).any(axis=1))[0]
+    bad_v = np.nonzero((ve[live] != vd[live]).any(axis=1))[0]
+    assert bad_k.size == 0, f"{what}: {bad_k.size} K rows differ, first slot {live[bad_k[0]]}"
+    assert bad_v.size == 0, f"{what}: {bad_v.size} V rows differ, first slot {live[bad_v[0]]}"
+    ks, vs = head.k_scale(), head.v_scale()
+    assert (exported["k_scale"][live].view(np.uint32) == ks[live].view(np.uint32)).all(), f"{what}: K scales differ"
+    assert (exported["v_scale"][live].view(np.uint32) == vs[live].view(np.uint32)).all(), f"{what}: V scales differ"
+    assert (exported["signs"] == head.signs()).all(), f"{what}: signs differ"

@@ -386,6 +386,16 @@ bool append_device(Group *g, const float *dk, const float *dv, int head0, int he
 // ---------------------------------------------------------------------------
 size_t partial_floats(const CacheView &c) { return (size_t)2 + c.padded; }
 
+// The general kernel's dynamic shared memory limit only ever grows (per device).
+bool ensure_general_smem(Group *g, size_t smem) {
+  static int smem_set[64] = {};
+  if ((int)smem > smem_set[g->device & 63]) {
+    CUDA_TRY(cudaFuncSetAttribute(compute_general_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute");
+    smem_set[g->device & 63] = (int)smem;
+  }
+  return true;
+}
+
 bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *partial_out) {
   const CacheView &c = g->c;
   const bool mirror = a.use_mirror != 0;
@@ -400,11 +410,7 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
   const int kcb = k_f32 ? 0 : (1 << c.k_bits);
   size_t smem = cg_smem_floats(c.padded, kcb, a.chunk) * sizeof(float);
-  static int smem_set[64] = {};
-  if ((int)smem > smem_set[g->device & 63]) {
-    CUDA_TRY(cudaFuncSetAttribute(compute_general_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute");
-    smem_set[g->device & 63] = (int)smem;
-  }
+  if (!ensure_general_smem(g, smem)) return false;
   const bool direct = a.n_splits == 1 && !want_partial_out;
   if (!direct) {
     if (!ensure_scratch(g, (size_t)a.n_splits * items * partial_floats(c) * sizeof(float))) return false;
@@ -432,6 +438,7 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
   const int items = a.heads_in_call * a.nq;
   const int ws = (int)round_up((size_t)a.n, 32);
   const size_t cells = (size_t)items * ws;
+  if (cells > (size_t)0x7fffffff) { set_error("compute: sparse-V workspace too large for one call"); return false; }
   size_t temp_bytes = 0;
   cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
                                                      (const int *)nullptr, (int *)nullptr, (int)cells, items,
@@ -451,11 +458,7 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
   a.n_splits = (a.n + a.span - 1) / a.span;
   a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
   size_t smem = cg_smem_floats(c.padded, 1 << c.k_bits, a.chunk) * sizeof(float);
-  static int smem_set[64] = {};
-  if ((int)smem > smem_set[g->device & 63]) {
-    CUDA_TRY(cudaFuncSetAttribute(compute_general_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute");
-    smem_set[g->device & 63] = (int)smem;
-  }
+  if (!ensure_general_smem(g, smem)) return false;
   compute_general_kernel<<<dim3(a.n_splits, a.heads_in_call, a.nq), CG_THREADS, smem, g->stream>>>(a);
   // 2. softmax weights, 3. stable descending sort per (head, query), 4. cut + accumulate
   softmax_weights_kernel<<<items, CG_THREADS, 0, g->stream>>>(w, o, ws, a.n);
@@ -493,32 +496,29 @@ bool stream_supported(const CacheView &c) {
   return false;
 }
 
-// Pick the number of KV spans per (head, query): spans are multiples of 256
-// tokens, at most CS_SPAN_MAX, and the item count should fill whole waves of
-// persistent blocks.
+// Pick the number of KV spans per (head, query): spans are multiples of 512
+// tokens (the largest stage tile), at most CS_SPAN_MAX, not needlessly short,
+// and the item count should fill whole waves of persistent blocks.
 void plan_spans(int n, int items_base, int sms, int &n_splits, int &span) {
+  const int G = 512;
+  const int n_pad = (int)round_up((size_t)n, G);
   const int min_splits = (n + CS_SPAN_MAX - 1) / CS_SPAN_MAX;
-  int best_s = min_splits;
   double best = -1.0;
+  n_splits = min_splits;
+  span = std::min(CS_SPAN_MAX, n_pad);
   for (int r = 1; r <= 16; ++r) {
-    int s = std::max(min_splits, (sms * r) / std::max(1, items_base));
-    s = std::max(1, s);
-    int sp = (int)round_up((size_t)(n + s - 1) / s, 256);
-    if (sp < 1024 && s > min_splits) {
-      sp = 1024;
-    }
+    int s = std::max(std::max(1, min_splits), (sms * r) / std::max(1, items_base));
+    int sp = (int)round_up((size_t)(n + s - 1) / s, G);
+    sp = std::max(sp, std::min(1024, n_pad));
     sp = std::min(sp, CS_SPAN_MAX);
-    int s2 = (n + sp - 1) / sp;
-    long long items = (long long)items_base * s2;
-    long long waves = (items + sms - 1) / sms;
-    double fill = (double)items / (double)(waves * sms);
-    double overhead = (double)sp / (double)(sp + 700); // per-item table build / bucket fold
-    double score = fill * overhead;
-    if (score > best + 1e-9) { best = score; best_s = s2; span = sp; }
+    const int s2 = (n + sp - 1) / sp;
+    const long long items = (long long)items_base * s2;
+    const long long waves = (items + sms - 1) / sms;
+    const double fill = (double)items / (double)(waves * sms);
+    const double overhead = (double)sp / (double)(sp + 700); // per-item table build / bucket fold
+    const double score = fill * overhead;
+    if (score > best + 1e-9) { best = score; n_splits = s2; span = sp; }
   }
-  n_splits = best_s;
-  span = (int)std::min<size_t>(CS_SPAN_MAX, round_up((size_t)(n + n_splits - 1) / n_splits, 256));
-  n_splits = (n + span - 1) / span;
 }
 
 bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, float *partial_out) {

@@ -66,9 +66,56 @@ __device__ __forceinline__ const float *item_src(const AppendLaunch &a, const It
 // ---------------------------------------------------------------------------
 // Register-resident path: one thread owns one vector (P floats in registers).
 // ---------------------------------------------------------------------------
+
+// Threshold search through a 41-entry shared-memory table keyed on the top
+// 12 bits of |v| (exponent + 3 mantissa bits, clamped to [0.125, 4.5)): every
+// such bucket holds at most one of the positive midpoints, so an entry is
+// {bits of that midpoint or 0xFFFFFFFF, number of midpoints below the bucket}.
+// With a = |v| (as an integer; one less for negative v, which turns the
+// comparison into the strict one the mirrored negative midpoints need),
+//   m = entry.count + (a >= entry.midpoint),  index = m ^ (v < 0 ? half-1 : half)
+// equals upstream's binary search (core/codebook.cpp:119-144) for every
+// non-NaN v.  Used only on vectors where NaN cannot occur.
+constexpr uint32_t QT_KEY_LO = 0x3E0u; // 0.125f >> 20
+constexpr uint32_t QT_KEY_HI = 0x408u; // 4.0f   >> 20
+constexpr int QT_ENTRIES = (int)(QT_KEY_HI - QT_KEY_LO) + 1;
+
+template <int BITS> __device__ __forceinline__ void build_quant_table(uint2 *qtab, int tid) {
+  constexpr int HALF = 1 << (BITS - 1);
+  if (tid < QT_ENTRIES) {
+    const uint32_t key = QT_KEY_LO + (uint32_t)tid;
+    const uint32_t lo = key << 20, hi = (key + 1u) << 20;
+    uint32_t m = 0, thr = 0xFFFFFFFFu;
+    for (int k = 0; k < HALF - 1; ++k) {
+      const uint32_t pk = __float_as_uint(c_thr[BITS - 2][HALF + k]);
+      if (pk < lo) ++m;
+      else if (pk < hi) thr = pk;
+    }
+    qtab[tid] = make_uint2(thr, m);
+  }
+}
+
+template <int BITS> __device__ __forceinline__ uint32_t quantize_lookup(float v, uint32_t qtab_addr) {
+  constexpr uint32_t HALF = 1u << (BITS - 1);
+  const bool neg = v < 0.0f;
+  uint32_t a = __float_as_uint(v) & 0x7FFFFFFFu;
+  a -= neg ? 1u : 0u;
+  uint32_t key = a >> 20;
+  key = min(max(key, QT_KEY_LO), QT_KEY_HI);
+  uint2 e;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "r"(qtab_addr + (key - QT_KEY_LO) * 8u));
+  const uint32_t m = e.y + (a >= e.x ? 1u : 0u);
+  return m ^ (neg ? HALF - 1u : HALF);
+}
+
+// Place index q of coordinate k (0-based within a packed group) into `word`.
+template <int BITS> __device__ __forceinline__ uint32_t index_shift(int k) {
+  return BITS == 4 ? (uint32_t)(8 * (k >> 1) + ((k & 1) ? 0 : 4)) : (uint32_t)(8 * (k >> 2) + (6 - 2 * (k & 3)));
+}
+
 template <int P, int BITS>
 __device__ __forceinline__ float quantize_row_regs(float (&x)[P], const uint32_t (&sg)[(P + 31) / 32],
-                                                   uint32_t (&w)[(P * BITS + 31) / 32]) {
+                                                   uint32_t (&w)[(P * BITS + 31) / 32], uint32_t qtab_addr) {
   // L2 norm: sequential, multiply and add rounded separately (core/quantizer.cpp:59-66)
   float norm = 0.f;
 #pragma unroll
@@ -98,48 +145,56 @@ __device__ __forceinline__ float quantize_row_regs(float (&x)[P], const uint32_t
   const float sq = __fsqrt_rn((float)P);
   const float isq = __fdiv_rn(1.0f, sq);
   // x * (1/sqrt p) [core/fwht.cpp:60-65]  then * sqrt p [core/quantizer.cpp:73-75]
+#pragma unroll
+  for (int i = 0; i < P; ++i) x[i] = __fmul_rn(__fmul_rn(x[i], isq), sq);
+
+  // The +-3 sigma clip (core/quantizer.cpp:81-89) can only change an index when
+  // 3*sigma falls below the largest midpoint (2.1476).  sigma^2 equals
+  // (norm^2 - 1e-12)/norm^2 up to rounding, so for norm >= 1e-5 it is >= 0.98 and
+  // the clip is a no-op; a finite norm also rules out NaN.  Everything else
+  // (tiny, infinite or NaN norms) takes the literal path below.
+  const bool plain = norm >= 1e-5f && norm < INFINITY;
+  if (plain) {
+    if (BITS == 3) {
+#pragma unroll
+      for (int i = 0; i < P; i += 32) {
+        uint32_t r[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t v24 = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v24 |= quantize_lookup<3>(x[i + g * 8 + k], qtab_addr) << (21 - 3 * k);
+          r[g] = __byte_perm(v24, 0, 0x3012);
+        }
+        w[(i >> 5) * 3 + 0] = r[0] | (r[1] << 24);
+        w[(i >> 5) * 3 + 1] = (r[1] >> 8) | (r[2] << 16);
+        w[(i >> 5) * 3 + 2] = (r[2] >> 16) | (r[3] << 8);
+      }
+    } else {
+      constexpr int PER = 32 / BITS;
+#pragma unroll
+      for (int i = 0; i < P; i += PER) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) word |= quantize_lookup<BITS>(x[i + k], qtab_addr) << index_shift<BITS>(k);
+        w[i / PER] = word;
+      }
+    }
+    return norm;
+  }
+
   float sum2 = 0.f;
 #pragma unroll
-  for (int i = 0; i < P; ++i) {
-    x[i] = __fmul_rn(__fmul_rn(x[i], isq), sq);
-    sum2 = __fadd_rn(sum2, __fmul_rn(x[i], x[i]));
-  }
-  // +-3 sigma clip, core/quantizer.cpp:81-89
+  for (int i = 0; i < P; ++i) sum2 = __fadd_rn(sum2, __fmul_rn(x[i], x[i]));
   const float sigma = __fsqrt_rn(__fadd_rn(__fdiv_rn(sum2, (float)P), 1e-12f));
   const float clip = __fmul_rn(3.0f, sigma);
   const float nclip = -clip;
-#pragma unroll
-  for (int i = 0; i < (P * BITS + 31) / 32; ++i) w[i] = 0;
-  if (BITS == 4) {
-#pragma unroll
-    for (int i = 0; i < P; i += 8) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        float v = x[i + k];
-        if (v > clip) v = clip;
-        if (v < nclip) v = nclip;
-        uint32_t q = (uint32_t)quantize_value<4>(v);
-        // byte k/2 of the word, high nibble first
-        word |= q << (8 * (k >> 1) + ((k & 1) ? 0 : 4));
-      }
-      w[i >> 3] = word;
-    }
-  } else if (BITS == 2) {
-#pragma unroll
-    for (int i = 0; i < P; i += 16) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        float v = x[i + k];
-        if (v > clip) v = clip;
-        if (v < nclip) v = nclip;
-        uint32_t q = (uint32_t)quantize_value<2>(v);
-        word |= q << (8 * (k >> 2) + (6 - 2 * (k & 3)));
-      }
-      w[i >> 4] = word;
-    }
-  } else { // 3 bits: 8 indices -> 3 bytes, big-endian bit order
+  auto clipped = [&](float v) {
+    if (v > clip) v = clip;
+    if (v < nclip) v = nclip;
+    return v;
+  };
+  if (BITS == 3) { // 8 indices -> 3 bytes, big-endian bit order
 #pragma unroll
     for (int i = 0; i < P; i += 32) {
       uint32_t r[4];
@@ -147,18 +202,22 @@ __device__ __forceinline__ float quantize_row_regs(float (&x)[P], const uint32_t
       for (int g = 0; g < 4; ++g) {
         uint32_t v24 = 0;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          float v = x[i + g * 8 + k];
-          if (v > clip) v = clip;
-          if (v < nclip) v = nclip;
-          v24 |= (uint32_t)quantize_value<3>(v) << (21 - 3 * k);
-        }
-        // memory image of the three bytes (p0 first) as a little-endian integer
-        r[g] = __byte_perm(v24, 0, 0x3012);
+        for (int k = 0; k < 8; ++k) v24 |= (uint32_t)quantize_value<3>(clipped(x[i + g * 8 + k])) << (21 - 3 * k);
+        r[g] = __byte_perm(v24, 0, 0x3012); // memory image of the three bytes, p0 first
       }
       w[(i >> 5) * 3 + 0] = r[0] | (r[1] << 24);
       w[(i >> 5) * 3 + 1] = (r[1] >> 8) | (r[2] << 16);
       w[(i >> 5) * 3 + 2] = (r[2] >> 16) | (r[3] << 8);
+    }
+  } else {
+    constexpr int PER = 32 / BITS;
+#pragma unroll
+    for (int i = 0; i < P; i += PER) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < PER; ++k)
+        word |= (uint32_t)quantize_value<BITS>(clipped(x[i + k])) << index_shift<BITS>(k);
+      w[i / PER] = word;
     }
   }
   return norm;
@@ -174,8 +233,11 @@ append_rows_kernel(const AppendLaunch a) {
   extern __shared__ __align__(128) unsigned char smem_rows[];
   float *tile = reinterpret_cast<float *>(smem_rows);
   __shared__ __align__(8) uint64_t bar;
+  __shared__ __align__(16) uint2 qtab[QT_ENTRIES + 7];
 
   const int tid = threadIdx.x;
+  if constexpr (BITS != 16) build_quant_table<BITS>(qtab, tid);
+  const uint32_t qtab_addr = smem_u32(qtab);
   const long long n_items = (long long)a.heads_in_call * a.n_tokens;
   const long long n_tiles = (n_items + THREADS - 1) / THREADS;
   const int dim = a.c.dim;
@@ -255,7 +317,7 @@ append_rows_kernel(const AppendLaunch a) {
 #pragma unroll
       for (int i = 0; i < (P + 31) / 32; ++i) sg[i] = c.signs[(size_t)p.h * c.sign_words + i];
       uint32_t w[NW];
-      float norm = quantize_row_regs<P, QB>(x, sg, w);
+      float norm = quantize_row_regs<P, QB>(x, sg, w, qtab_addr);
       uint8_t *row = slab + (size_t)p.h * stride + (size_t)p.slot * (NW * 4);
       if ((NW * 4) % 16 == 0) {
         uint4 *d4 = reinterpret_cast<uint4 *>(row);

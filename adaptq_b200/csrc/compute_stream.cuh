@@ -7,7 +7,7 @@
 // organised for HBM streaming on sm_100a:
 //
 //  * persistent blocks, one per SM; a work item is (head, query, KV span);
-//  * a producer warp feeds a ring of 8 KB shared-memory stages with bulk
+//  * a producer warp feeds a ring of 16 KB shared-memory stages with bulk
 //    (TMA) copies, first the span's K rows, then its V rows -- K and V are
 //    separate slabs and are read as separate streams; the producer runs ahead
 //    across phase and item boundaries so HBM never waits for arithmetic;
@@ -23,7 +23,10 @@
 //    token is added into bucket[byte][column]; after the span, each output
 //    coordinate is the centroid-weighted sum of its column's 256 buckets.
 //    That costs one shared-memory reduction per packed byte (4 coordinates at
-//    2 bits) instead of one multiply-add per coordinate;
+//    2 bits) instead of one multiply-add per coordinate.  The buckets are
+//    32-bit fixed point (the span's weights are scaled so that they sum to
+//    2^30): integer shared-memory reductions are native and order-independent,
+//    so the result is deterministic; floating-point ones are not native;
 //  * one inverse Walsh-Hadamard transform at the end (or in the merge kernel
 //    when the sequence is split).
 //
@@ -33,10 +36,11 @@
 
 namespace aq {
 
-constexpr int CS_CONSUMERS = 256;           // 8 consumer warps
+constexpr int CS_CONSUMERS = 512;           // 16 consumer warps
+constexpr int CS_WARPS = CS_CONSUMERS / 32;
 constexpr int CS_THREADS = CS_CONSUMERS + 32; // + 1 producer warp
-constexpr int CS_STAGE_BYTES = 8192;
-constexpr int CS_STAGES = 6;
+constexpr int CS_STAGE_BYTES = 16384;
+constexpr int CS_STAGES = 3;
 constexpr int CS_SPAN_MAX = 8192;           // tokens per work item (scores kept in shared memory)
 constexpr int CS_TABLE_BYTES = 65536;       // [256][64] floats
 constexpr size_t CS_SMEM_BYTES = 65536 /* alignment slack, holds the ring */ + CS_TABLE_BYTES /* K table */ +
@@ -48,19 +52,21 @@ struct StreamLaunch {
   float *out;     // [heads_in_call][nq][dim]                 (n_splits == 1)
   float *partial; // [n_splits][heads_in_call*nq][2+P]        (n_splits  > 1)
   int head0, heads_in_call, nq;
-  int n, n_splits, span; // span: tokens per split, multiple of 256
+  int n, n_splits, span; // span: tokens per split, multiple of 512
   int force_partial;     // write the partial even when there is a single span
   int *status;
 };
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CS_CONSUMERS) : "memory"); }
+// Not volatile: the address always derives from data loaded after the
+// barrier that published it, so the compiler is free to schedule these.
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ void red_shared_add(uint32_t addr, float v) {
-  asm volatile("red.shared.add.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void red_shared_add(uint32_t addr, uint32_t v) {
+  asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float consumer_reduce(float v, float *red, bool is_max) {
@@ -71,7 +77,7 @@ __device__ __forceinline__ float consumer_reduce(float v, float *red, bool is_ma
   consumer_sync();
   float r = red[0];
 #pragma unroll
-  for (int i = 1; i < CS_CONSUMERS / 32; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+  for (int i = 1; i < CS_WARPS; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
   return r;
 }
 
@@ -123,7 +129,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   static_assert(P == VW * 32 / VB, "K and V rows must describe the same padded dimension");
   constexpr int KROW = KW * 4, VROW = VW * 4;
   constexpr int TKN = CS_STAGE_BYTES / KROW, TVN = CS_STAGE_BYTES / VROW; // tokens per stage
-  constexpr int KSTEPS = TKN / 8 / 4, VSTEPS = TVN / 8 / 4;                 // 4 tokens per warp step
+  constexpr int KSTEPS = TKN / CS_WARPS / 4, VSTEPS = TVN / CS_WARPS / 4;   // 4 tokens per warp step
   constexpr int KWPL = KW / 8, VWPL = VW / 8;                               // words per lane
   constexpr int KC = KW * 4, VC = VW * 4;                                   // byte columns
   constexpr int KE = 8 / KB, VE = 8 / VB;                                   // coordinates per byte
@@ -136,8 +142,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   const uint32_t front = table_addr - base;
   unsigned char *table_p = smem + front;
   const uint32_t bucket_addr = table_addr + CS_TABLE_BYTES;
-  float *bucket = reinterpret_cast<float *>(table_p + CS_TABLE_BYTES);
-  float *sc = bucket + CS_TABLE_BYTES / 4;
+  uint32_t *bucket = reinterpret_cast<uint32_t *>(table_p + CS_TABLE_BYTES);
+  float *sc = reinterpret_cast<float *>(bucket + CS_TABLE_BYTES / 4);
   unsigned char *misc = reinterpret_cast<unsigned char *>(sc + CS_SPAN_MAX);
   float *qr = reinterpret_cast<float *>(misc);          // P floats (<= 512 B)
   float *red = qr + 128;                                 // 64 floats
@@ -156,7 +162,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   if (tid == 0) {
     for (int s = 0; s < CS_STAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], CS_CONSUMERS / 32);
+      mbar_init(&empty[s], CS_WARPS);
     }
     *s_fail = layout_ok ? 0 : 2;
     fence_barrier_init();
@@ -208,9 +214,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   for (int m = 0; m < KWPL; ++m) kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
 #pragma unroll
   for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
-  // V buckets: with 32 byte columns the array has room for two copies; warps
-  // 4..7 use the second one (columns 32..63) to halve collisions.
-  const int vcol_off = (VC == 32 && warp >= 4) ? 32 : 0;
+  // V buckets: with 32 byte columns the array has room for two copies; the
+  // upper half of the warps uses the second one (columns 32..63).
+  const int vcol_off = (VC == 32 && warp >= CS_WARPS / 2) ? 32 : 0;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int kk = (k + tq) & 3;
@@ -258,10 +264,11 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     consumer_butterflies(qr, P);
     if (tid < P) qr[tid] = qr[tid] * isp * (sqrtf((float)P) * qn);
     // ---- zero the buckets, build the K byte table ---------------------------
-    for (int i = tid; i < CS_TABLE_BYTES / 4; i += CS_CONSUMERS) bucket[i] = 0.f;
+    for (int i = tid; i < CS_TABLE_BYTES / 4; i += CS_CONSUMERS) bucket[i] = 0u;
     consumer_sync();
     {
-      // thread -> column (consecutive lanes, consecutive banks), a quarter of the byte values
+      // thread -> column (consecutive lanes, consecutive banks), a slice of the byte values
+      constexpr int HPT = 16 / (CS_CONSUMERS / 64); // high-nibble values per thread
       const int col = tid & 63, bq = tid >> 6;
       if (col < KC) {
         if (KE == 2) {
@@ -270,8 +277,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
           for (int i = 0; i < 16; ++i) lo[i] = q1 * kcb[i];
 #pragma unroll
-          for (int hi = 0; hi < 4; ++hi) {
-            const int hv = bq * 4 + hi;
+          for (int hi = 0; hi < HPT; ++hi) {
+            const int hv = bq * HPT + hi;
             const float av = q0 * kcb[hv];
 #pragma unroll
             for (int i = 0; i < 16; ++i) table[(hv * 16 + i) * 64 + col] = av + lo[i];
@@ -282,8 +289,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
           for (int i = 0; i < 16; ++i) t23[i] = q2 * kcb[i >> 2] + q3 * kcb[i & 3];
 #pragma unroll
-          for (int hi = 0; hi < 4; ++hi) {
-            const int hv = bq * 4 + hi;
+          for (int hi = 0; hi < HPT; ++hi) {
+            const int hv = bq * HPT + hi;
             const float t01 = q0 * kcb[hv >> 2] + q1 * kcb[hv & 3];
 #pragma unroll
             for (int i = 0; i < 16; ++i) table[(hv * 16 + i) * 64 + col] = t01 + t23[i];
@@ -297,15 +304,22 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     for (int t = t0; t < t1; t += TKN) {
       wait_full();
       const uint32_t st_addr = smem_u32(ring + (size_t)stage * CS_STAGE_BYTES);
+      const uint32_t *stw = reinterpret_cast<const uint32_t *>(ring + (size_t)stage * CS_STAGE_BYTES);
+      (void)st_addr;
+      uint32_t dk[KSTEPS][KWPL];
+#pragma unroll
+      for (int s = 0; s < KSTEPS; ++s) {
+        const int tok = warp * (TKN / CS_WARPS) + 4 * s + tq; // token within the stage
+#pragma unroll
+        for (int m = 0; m < KWPL; ++m) dk[s][m] = stw[tok * KW + kword[m]];
+      }
       float pv[KSTEPS];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
-        const int tok = warp * (TKN / 8) + 4 * s + tq; // token within the stage
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
         for (int m = 0; m < KWPL; ++m) {
-          uint32_t d;
-          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(d) : "r"(st_addr + tok * KROW + kword[m] * 4));
+          const uint32_t d = dk[s][m];
           a0 += lds_f32(__byte_perm(d, kconst[m][0], ksel[0]));
           a1 += lds_f32(__byte_perm(d, kconst[m][1], ksel[1]));
           a0 += lds_f32(__byte_perm(d, kconst[m][2], ksel[2]));
@@ -315,7 +329,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       }
       const float total = group_transpose_sum<KSTEPS>(pv, wl);
       const int step = KSTEPS == 8 ? wl : (wl >> 1);
-      const int tok = warp * (TKN / 8) + 4 * step + tq;
+      const int tok = warp * (TKN / CS_WARPS) + 4 * step + tq;
       if ((KSTEPS == 8 || (wl & 1) == 0) && t + tok < t1) sc[t - t0 + tok] = total;
       release();
     }
@@ -331,7 +345,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       mx = fmaxf(mx, s);
     }
     mx = consumer_reduce(mx, red, true);
-    float ls = 0.f;
+    float ls = 0.f, wsum = 0.f;
     const int len_pad = min(CS_SPAN_MAX, (len + TVN - 1) / TVN * TVN);
     for (int i = tid; i < len_pad; i += CS_CONSUMERS) {
       float w = 0.f;
@@ -339,25 +353,38 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         const float e = expf(sc[i] - mx);
         ls += e;
         w = e * vsc[i] * isp;
+        wsum += w;
       }
       sc[i] = w;
     }
     ls = consumer_reduce(ls, red, false);
+    wsum = consumer_reduce(wsum, red, false);
+    // weights -> 32-bit fixed point with the span's total mapped to 2^30, so no
+    // bucket can overflow and the rounding error is below 2^-31 of the total per token
+    const float fx = (wsum > 0.f && wsum < INFINITY) ? 1073741824.0f / wsum : 0.f;
+    const float inv_fx = fx > 0.f ? wsum * (1.0f / 1073741824.0f) : 0.f;
+    uint32_t *scu = reinterpret_cast<uint32_t *>(sc);
+    for (int i = tid; i < len_pad; i += CS_CONSUMERS) scu[i] = __float2uint_rn(sc[i] * fx);
+    consumer_sync();
 
     // ---- V stream: add each token's weight into bucket[byte][column] ---------------------
     for (int t = t0; t < t1; t += TVN) {
       wait_full();
-      const uint32_t st_addr = smem_u32(ring + (size_t)stage * CS_STAGE_BYTES);
+      const uint32_t *stw = reinterpret_cast<const uint32_t *>(ring + (size_t)stage * CS_STAGE_BYTES);
+      uint32_t dv[VSTEPS][VWPL], wv[VSTEPS];
 #pragma unroll
       for (int s = 0; s < VSTEPS; ++s) {
-        const int tok = warp * (TVN / 8) + 4 * s + tq;
-        const float w = sc[t - t0 + tok];
+        const int tok = warp * (TVN / CS_WARPS) + 4 * s + tq;
+        wv[s] = scu[t - t0 + tok];
+#pragma unroll
+        for (int m = 0; m < VWPL; ++m) dv[s][m] = stw[tok * VW + vword[m]];
+      }
+#pragma unroll
+      for (int s = 0; s < VSTEPS; ++s) {
 #pragma unroll
         for (int m = 0; m < VWPL; ++m) {
-          uint32_t d;
-          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(d) : "r"(st_addr + tok * VROW + vword[m] * 4));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) red_shared_add(__byte_perm(d, vconst[m][k], ksel[k]), w);
+          for (int k = 0; k < 4; ++k) red_shared_add(__byte_perm(dv[s][m], vconst[m][k], ksel[k]), wv[s]);
         }
       }
       release();
@@ -373,10 +400,11 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       const int shift = 8 - VB * (e + 1);
       float av = 0.f;
       for (int b = part; b < 256; b += PARTS) {
-        float bv = bucket[b * 64 + col];
-        if (VC == 32) bv += bucket[b * 64 + 32 + col];
-        av += bv * vcb[(b >> shift) & ((1 << VB) - 1)];
+        uint32_t bi = bucket[b * 64 + col];
+        if (VC == 32) bi += bucket[b * 64 + 32 + col];
+        av += (float)bi * vcb[(b >> shift) & ((1 << VB) - 1)];
       }
+      av *= inv_fx;
       consumer_sync(); // all bucket reads done before sc[] is reused as fold space
       sc[tid] = av;
       consumer_sync();

@@ -1,0 +1,382 @@
+#!/usr/bin/env python
+"""Benchmark of the AdapTQ decode hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (BASELINE.json configs[3], the configuration the metric is quoted on):
+batched decode at Llama-3-8B KV shape -- 256 independent sequences x 32 layers
+x 8 KV heads = 65 536 head-instances per GPU, head dim 128, context 8192,
+K 4-bit / V 2-bit, dense V, no hybrid window.  K/V are N(0,1) with 1 % of the
+entries replaced by N(0,20) outliers (synthetic; no dataset is involved).
+
+One step = one decode step of every sequence: append the new token's K and V
+to every head (the ring is full, so the oldest token is evicted) and run
+decode attention for one query per head.  value = sequences * steps / time
+(tokens/s, all ranks).  Under torchrun every rank holds its own 256 sequences
+(weak scaling, no collective on the data path).
+
+The line also carries:
+  e2e          the same step driven from pinned HOST buffers through the C ABI
+               (H2D of K, V, q and D2H of the outputs inside the timed region)
+  roofline     streaming decode kernel: algorithmic KV bytes / measured kernel time
+               against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
+  append       bulk-append kernel throughput (vectors/s) and its roofline
+  cpu_baseline the upstream CPU implementation on this host's cores (bounded sample)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SEQS, LAYERS, KV_HEADS, DIM, CONTEXT = 256, 32, 8, 128, 8192
+K_BITS, V_BITS = 4, 2
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seqs", type=int, default=SEQS, help="sequences per GPU (default: the BASELINE config)")
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--mode", default="decode", choices=["decode", "append"],
+                    help="append: run only the bulk-append kernel benchmark and print its JSON")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-append-bench", action="store_true")
+    ap.add_argument("--cpu-sample-heads", type=int, default=0)
+    return ap.parse_args()
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# --------------------------------------------------------------------------
+# clocks sampled during the timed region (NVML, read-only)
+# --------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if r & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def start(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------
+# CPU arm: the upstream implementation (oracle/_ref) on the host cores
+# --------------------------------------------------------------------------
+def cpu_arm(n_heads_sample: int, context: int, steps: int, warmup: int, seqs: int, threads: int):
+    """Times the upstream CPU build on `n_heads_sample` head-instances of the same
+    shape and distribution, scales linearly to the full head count (heads are
+    independent).  Returns (tokens_per_s, description dict)."""
+    import numpy as np
+    from oracle import loader
+    kind = "reference" if loader.ref_available(fast=True) else "port"
+    rng = np.random.default_rng(1234)
+    shape = (n_heads_sample, context, DIM)
+    keys = rng.standard_normal(shape, dtype=np.float32)
+    vals = rng.standard_normal(shape, dtype=np.float32)
+    for a in (keys, vals):
+        m = rng.random(shape) < 0.01
+        a[m] = (rng.standard_normal(int(m.sum())) * 20.0).astype(np.float32)
+    q = rng.standard_normal((n_heads_sample, DIM), dtype=np.float32)
+    total_heads = seqs * LAYERS * KV_HEADS
+    if kind == "reference":
+        loader.time_reference_heads(min(n_heads_sample, threads), DIM, K_BITS, V_BITS, 64, 42,
+                                    keys[:threads, :64], vals[:threads, :64], q[:threads], max(1, warmup), threads)
+        t_app, t_cmp, _ = loader.time_reference_heads(n_heads_sample, DIM, K_BITS, V_BITS, context, 42, keys, vals, q,
+                                                      steps, threads)
+    else:  # the C restatement, single thread
+        threads = 1
+        O = loader.oracle()
+        hs = [loader.Head(O, DIM, K_BITS, V_BITS, context, loader.mha_head_seed(42, h)) for h in range(n_heads_sample)]
+        t0 = time.perf_counter()
+        for h, hd in enumerate(hs):
+            hd.append_many(keys[h], vals[h])
+        t_app = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            for h, hd in enumerate(hs):
+                hd.compute(q[h])
+        t_cmp = time.perf_counter() - t0
+    step_s = (t_cmp / steps) * (total_heads / n_heads_sample)
+    tok_s = seqs / step_s
+    desc = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": kind,
+            "sample": f"{n_heads_sample} of {total_heads} head-instances (dim {DIM}, context {context}, K{K_BITS}/V{V_BITS}, "
+                      f"dense V), {steps} compute steps, scaled linearly by head count; "
+                      f"append {2 * n_heads_sample * context / t_app:.3g} vectors/s on the same cores",
+            "append_vectors_per_s": 2 * n_heads_sample * context / t_app,
+            "ms_per_step_scaled": step_s * 1e3}
+    return tok_s, desc
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import loader
+    threads = os.cpu_count() or 1
+    if loader.ref_available(fast=True):
+        threads = min(threads, loader.ref_max_threads())
+    n_sample = args.cpu_sample_heads or max(threads, 32)
+    tok_s, desc = cpu_arm(n_sample, args.context, max(1, args.steps), args.warmup, args.seqs, threads)
+    line = {"impl": "reference", "metric": "decode_attn_tokens_per_s", "value": tok_s, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": desc["ms_per_step_scaled"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args), "cpu_baseline": desc,
+            "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(args):
+    return {"workload": "batched decode, Llama-3-8B KV shape (BASELINE configs[3])", "sequences_per_gpu": args.seqs,
+            "layers": LAYERS, "kv_heads": KV_HEADS, "head_dim": DIM, "context": args.context, "k_bits": K_BITS,
+            "v_bits": V_BITS, "v_mass": 0.0, "hybrid_thresh": 0,
+            "step": "append 1 token to every head (ring full, FIFO eviction) + decode attention, 1 query per head",
+            "l2": "inputs larger than L2 (KV cache >> 126 MB per step)", "sharding": "sequences per rank, no collective"}
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def fill_cache(ctx, heads, context, torch, gen):
+    chunk = max(1, min(64, (1 << 28) // (heads * DIM)))  # <= 1 GiB per tensor
+    done = 0
+    while done < context:
+        t = min(chunk, context - done)
+        k = torch.randn((t, heads, DIM), device="cuda", generator=gen)
+        v = torch.randn((t, heads, DIM), device="cuda", generator=gen)
+        for a in (k, v):
+            m = torch.rand(a.shape, device="cuda", generator=gen) < 0.01
+            a[m] = torch.randn(int(m.sum().item()), device="cuda", generator=gen) * 20.0
+        ctx.append_all(k, v, done)
+        done += t
+    ctx.synchronize()
+
+
+def append_bench(torch, L, peak):
+    """BASELINE configs[3] bulk append: 32768 tokens x 8 heads x 128, K and V, bits 2/3/4."""
+    import adaptq_b200
+    out = {}
+    T, H = 32768, 8
+    k = torch.randn((T, H, DIM), device="cuda")
+    v = torch.randn((T, H, DIM), device="cuda")
+    for bits in (4, 3, 2):
+        ctx = adaptq_b200.MHAContext(H, DIM, bits, bits, T, seed=42, v_mass=0.0, hybrid_thresh=0)
+        for _ in range(3):
+            ctx.append_all(k, v)
+        torch.cuda.synchronize()
+        reps = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            ctx.append_all(k, v)
+        e1.record()
+        torch.cuda.synchronize()
+        s = e0.elapsed_time(e1) / 1e3 / reps
+        vecs = 2 * T * H
+        bytes_per_vec = 4 * DIM + DIM * bits // 8 + 4
+        out[f"k{bits}v{bits}"] = {"vectors_per_s": vecs / s, "us_per_call": s * 1e6,
+                                  "achieved_gbs": vecs * bytes_per_vec / s / 1e9,
+                                  "frac_of_peak": vecs * bytes_per_vec / s / 1e9 / peak,
+                                  "bytes_per_vector": bytes_per_vec}
+        ctx.close()
+    return {"workload": f"{T} tokens x {H} heads x {DIM}, K and V ({2 * T * H} vectors per call, 268 MB read: "
+                        "larger than L2)", "results": out}
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import adaptq_b200
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = adaptq_b200.load()
+    peak, peak_src = measured_peak()
+    if args.mode == "append":
+        if rank == 0:
+            print(json.dumps({"metric": "bulk_append_vectors_per_s", "append": append_bench(torch, L, peak)}))
+        return
+
+    heads = args.seqs * LAYERS * KV_HEADS
+    n = args.context
+    seeds = [(42 ^ layer) ^ (hd * 0xDEADBEEFCAFE) for _s in range(args.seqs) for layer in range(LAYERS)
+             for hd in range(KV_HEADS)]
+    ctx = adaptq_b200.MHAContext(heads, DIM, K_BITS, V_BITS, n, seeds=seeds, v_mass=0.0, hybrid_thresh=0)
+    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    fill_cache(ctx, heads, n, torch, gen)
+
+    # device-resident inputs for `value`, pinned host inputs for `e2e`
+    d_k = torch.randn((heads, DIM), device="cuda", generator=gen)
+    d_v = torch.randn((heads, DIM), device="cuda", generator=gen)
+    d_q = torch.randn((heads, DIM), device="cuda", generator=gen)
+    d_o = torch.empty((heads, DIM), device="cuda")
+    h_k, h_v, h_q = (t.cpu().pin_memory() for t in (d_k, d_v, d_q))
+    h_o = torch.empty((heads, DIM)).pin_memory()
+
+    def step_device():
+        ctx.append_all(d_k, d_v)
+        ctx.compute_all(d_q, out=d_o)
+
+    def step_host():
+        ctx.append_all(h_k, h_v)
+        ctx.compute_all(h_q, out=h_o)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps, with_kernel_events=False):
+        evs = []
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        launches0 = L.adaptq_kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            if with_kernel_events:
+                ctx.append_all(d_k, d_v)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                ctx.compute_all(d_q, out=d_o)
+                b.record()
+                evs.append((a, b))
+            else:
+                fn()
+        e1.record()
+        barrier()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        kern_ms = [a.elapsed_time(b) for a, b in evs]
+        return ms, clocks, L.adaptq_kernel_launches() - launches0, kern_ms
+
+    for _ in range(max(3, args.warmup)):
+        step_device()
+    ms, clocks, launches, kern_ms = timed(step_device, args.steps, with_kernel_events=True)
+    ctx.synchronize()
+    for _ in range(2):
+        step_host()
+    ms_h, clocks_h, _, _ = timed(step_host, args.steps)
+    ctx.synchronize()
+
+    seqs_total = args.seqs * world
+    value = seqs_total * args.steps / (ms / 1e3)
+    e2e = seqs_total * args.steps / (ms_h / 1e3)
+    alg_bytes = heads * (n * (DIM * K_BITS // 8 + DIM * V_BITS // 8 + 8) + 8 * DIM)
+    kt = sum(kern_ms) / len(kern_ms) / 1e3
+    roof = {"bound": "hbm", "kernel": "compute_stream_kernel<K4,V2,dim128>", "achieved": alg_bytes / kt / 1e9,
+            "peak": peak, "unit": "GB/s", "frac": alg_bytes / kt / 1e9 / peak, "peak_source": peak_src,
+            "traffic": None, "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kt * 1e3,
+            "of_nominal_8TBs": alg_bytes / kt / 8e12}
+
+    line = {"metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args), "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 3 * heads * DIM * 4,
+                    "d2h_bytes_per_step": heads * DIM * 4, "ms_per_step": ms_h / args.steps, "clocks": clocks_h},
+            "gpu_launches": int(launches), "roofline": roof,
+            "effective_kv_gbs": alg_bytes * world / (ms / args.steps / 1e3) / 1e9}
+    ctx.close()
+    del ctx
+    torch.cuda.empty_cache()
+    if rank == 0:
+        if not args.skip_append_bench:
+            try:
+                line["append"] = append_bench(torch, L, peak)
+            except Exception as ex:  # the headline must still print
+                line["append"] = {"error": repr(ex)}
+        if not args.skip_cpu_baseline and world == 1:
+            try:
+                threads = os.cpu_count() or 1
+                from oracle import loader
+                if loader.ref_available(fast=True):
+                    threads = min(threads, loader.ref_max_threads())
+                _, desc = cpu_arm(args.cpu_sample_heads or max(threads, 32), n, 4, 1, args.seqs, threads)
+                line["cpu_baseline"] = desc
+            except Exception as ex:
+                line["cpu_baseline"] = {"error": repr(ex)}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

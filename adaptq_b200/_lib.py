@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libadaptq_b200.so")
+LIB_PATH = os.environ.get("ADAPTQ_B200_LIB") or os.path.join(_HERE, "libadaptq_b200.so")
 
 f32p = C.POINTER(C.c_float)
 u8p = C.POINTER(C.c_uint8)

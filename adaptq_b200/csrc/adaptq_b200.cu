@@ -304,7 +304,7 @@ bool check_status(Group *g, const char *fn) {
 template <int P, int BITS>
 bool launch_rows(Group *g, const AppendLaunch &a) {
   constexpr int THREADS = 128;
-  constexpr size_t SMEM = (size_t)THREADS * (P + 4) * sizeof(float);
+  constexpr size_t SMEM = ((size_t)THREADS * (P + 4) + (size_t)(THREADS / 32) * P) * sizeof(float);
   static bool configured[64] = {};
   auto kern = append_rows_kernel<P, BITS, THREADS>;
   if (!configured[g->device & 63]) {
@@ -521,11 +521,19 @@ void plan_spans(int n, int items_base, int sms, int &n_splits, int &span) {
   }
 }
 
+#ifdef AQ_PROBE
+static unsigned long long *g_probe = nullptr;
+#endif
+
 bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, float *partial_out) {
   const CacheView &c = g->c;
   StreamLaunch a{};
   a.c = c; a.q = ca.q; a.out = ca.out; a.head0 = ca.head0; a.heads_in_call = ca.heads_in_call; a.nq = ca.nq;
   a.n = ca.n; a.status = g->d_status;
+#ifdef AQ_PROBE
+  if (!g_probe) { cudaMalloc(&g_probe, 64); cudaMemset(g_probe, 0, 64); }
+  a.probe = g_probe;
+#endif
   const int items_base = a.heads_in_call * a.nq;
   plan_spans(a.n, items_base, g->sm_count, a.n_splits, a.span);
   const bool direct = a.n_splits == 1 && !want_partial_out;
@@ -997,5 +1005,15 @@ int adaptq_mha_export_head(adaptq_mha_t h, int head_idx, uint8_t *k_rows, uint8_
   if (mirror_tokens) *mirror_tokens = st.mirror;
   return 0;
 }
+
+#ifdef AQ_PROBE
+int adaptq_probe_read(unsigned long long *out, int reset) {
+  if (!g_probe) return -1;
+  cudaDeviceSynchronize();
+  cudaMemcpy(out, g_probe, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  if (reset) cudaMemset(g_probe, 0, 8 * sizeof(unsigned long long));
+  return 0;
+}
+#endif
 
 } // extern "C"

@@ -36,11 +36,22 @@
 
 namespace aq {
 
+#ifdef AQ_PROBE
+#define AQ_MARK(k)                                     \
+  if (tid == 0) {                                      \
+    long long now__ = clock64();                       \
+    probe_acc[k] += (unsigned long long)(now__ - probe_last); \
+    probe_last = now__;                                \
+  }
+#else
+#define AQ_MARK(k)
+#endif
+
 constexpr int CS_CONSUMERS = 512;           // 16 consumer warps
 constexpr int CS_WARPS = CS_CONSUMERS / 32;
 constexpr int CS_THREADS = CS_CONSUMERS + 32; // + 1 producer warp
 constexpr int CS_STAGE_BYTES = 16384;
-constexpr int CS_STAGES = 3;
+constexpr int CS_MAX_STAGES = 6;             // ring stages: as many as fit beside the tables (3..5)
 constexpr int CS_SPAN_MAX = 8192;           // tokens per work item (scores kept in shared memory)
 constexpr int CS_TABLE_BYTES = 65536;       // [256][64] floats
 constexpr size_t CS_SMEM_BYTES = 65536 /* alignment slack, holds the ring */ + CS_TABLE_BYTES /* K table */ +
@@ -55,6 +66,9 @@ struct StreamLaunch {
   int n, n_splits, span; // span: tokens per split, multiple of 512
   int force_partial;     // write the partial even when there is a single span
   int *status;
+#ifdef AQ_PROBE
+  unsigned long long *probe; // per-phase cycle counters (diagnostic builds only)
+#endif
 };
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CS_CONSUMERS) : "memory"); }
@@ -79,6 +93,20 @@ __device__ __forceinline__ float consumer_reduce(float v, float *red, bool is_ma
 #pragma unroll
   for (int i = 1; i < CS_WARPS; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
   return r;
+}
+
+// Sum two values over all consumer threads at once.
+__device__ __forceinline__ void consumer_reduce2(float &a, float &b, float *red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  consumer_sync();
+  if (lane == 0) { red[warp] = a; red[32 + warp] = b; }
+  consumer_sync();
+  a = red[0];
+  b = red[32];
+#pragma unroll
+  for (int i = 1; i < CS_WARPS; ++i) { a += red[i]; b += red[32 + i]; }
 }
 
 __device__ __forceinline__ void consumer_butterflies(float *x, int p) {
@@ -133,7 +161,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   constexpr int KWPL = KW / 8, VWPL = VW / 8;                               // words per lane
   constexpr int KC = KW * 4, VC = VW * 4;                                   // byte columns
   constexpr int KE = 8 / KB, VE = 8 / VB;                                   // coordinates per byte
-  constexpr int RING_BYTES = CS_STAGES * CS_STAGE_BYTES;
+  constexpr int BUCKET_BYTES = VC * 1024;                                   // [256][VC] 32-bit buckets
 
   extern __shared__ __align__(1024) unsigned char smem_stream[];
   unsigned char *smem = smem_stream;
@@ -143,15 +171,24 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   unsigned char *table_p = smem + front;
   const uint32_t bucket_addr = table_addr + CS_TABLE_BYTES;
   uint32_t *bucket = reinterpret_cast<uint32_t *>(table_p + CS_TABLE_BYTES);
-  float *sc = reinterpret_cast<float *>(bucket + CS_TABLE_BYTES / 4);
+  float *sc = reinterpret_cast<float *>(table_p + CS_TABLE_BYTES + BUCKET_BYTES);
   unsigned char *misc = reinterpret_cast<unsigned char *>(sc + CS_SPAN_MAX);
   float *qr = reinterpret_cast<float *>(misc);          // P floats (<= 512 B)
   float *red = qr + 128;                                 // 64 floats
-  uint64_t *full = reinterpret_cast<uint64_t *>(red + 64);
-  uint64_t *empty = full + CS_STAGES;
-  int *s_fail = reinterpret_cast<int *>(empty + CS_STAGES);
-  unsigned char *ring = (front >= (uint32_t)RING_BYTES) ? smem : (misc + 2048);
-  const bool layout_ok = front >= (uint32_t)RING_BYTES || (65536u - front) >= (uint32_t)RING_BYTES + 0u;
+  float *s_cb = red + 64;                                // 16 floats: V centroids
+  uint64_t *full = reinterpret_cast<uint64_t *>(s_cb + 16);
+  uint64_t *empty = full + CS_MAX_STAGES;
+  int *s_fail = reinterpret_cast<int *>(empty + CS_MAX_STAGES);
+  // The ring lives in whatever is left: the slack in front of the 64 KB-aligned
+  // table and the tail behind the misc block.
+  unsigned char *back = misc + 2048;
+  const int n_front = min((int)(front / CS_STAGE_BYTES), CS_MAX_STAGES);
+  const int n_back = (int)((CS_SMEM_BYTES - front - CS_TABLE_BYTES - BUCKET_BYTES - CS_SPAN_MAX * 4 - 2048) / CS_STAGE_BYTES);
+  const int n_stages = min(n_front + n_back, CS_MAX_STAGES);
+  const bool layout_ok = n_stages >= 2;
+  auto stage_ptr = [&](int s) -> unsigned char * {
+    return s < n_front ? smem + (size_t)s * CS_STAGE_BYTES : back + (size_t)(s - n_front) * CS_STAGE_BYTES;
+  };
 
   const int tid = threadIdx.x;
   const CacheView &c = a.c;
@@ -160,11 +197,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   const int n_items = items_base * a.n_splits;
 
   if (tid == 0) {
-    for (int s = 0; s < CS_STAGES; ++s) {
+    for (int s = 0; s < CS_MAX_STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], CS_WARPS);
     }
     *s_fail = layout_ok ? 0 : 2;
+    for (int i = 0; i < 16; ++i) s_cb[i] = c_cb[VB - 2][i];
     fence_barrier_init();
   }
   __syncthreads();
@@ -194,8 +232,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
           }
           const uint32_t bytes = ((uint32_t)(min(tn, t1 - t) * rowb) + 15u) & ~15u;
           mbar_expect_tx(&full[stage], bytes);
-          bulk_g2s(ring + (size_t)stage * CS_STAGE_BYTES, src + (size_t)t * rowb, bytes, &full[stage]);
-          if (++stage == CS_STAGES) { stage = 0; phase ^= 1u; }
+          bulk_g2s(stage_ptr(stage), src + (size_t)t * rowb, bytes, &full[stage]);
+          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -214,9 +252,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   for (int m = 0; m < KWPL; ++m) kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
 #pragma unroll
   for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
-  // V buckets: with 32 byte columns the array has room for two copies; the
-  // upper half of the warps uses the second one (columns 32..63).
-  const int vcol_off = (VC == 32 && warp >= CS_WARPS / 2) ? 32 : 0;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int kk = (k + tq) & 3;
@@ -224,7 +259,11 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
     for (int m = 0; m < KWPL; ++m) kconst[m][k] = table_addr | (uint32_t)((4 * kword[m] + kk) << 2);
 #pragma unroll
-    for (int m = 0; m < VWPL; ++m) vconst[m][k] = bucket_addr | (uint32_t)((4 * vword[m] + kk + vcol_off) << 2);
+    // bucket rows are VC*4 bytes: with 64 columns the byte lands in address bits
+    // 8..15 directly; with 32 columns the address is formed doubled and halved after
+    for (int m = 0; m < VWPL; ++m)
+      vconst[m][k] = VC == 64 ? (bucket_addr | (uint32_t)((4 * vword[m] + kk) << 2))
+                              : ((bucket_addr << 1) | (uint32_t)((4 * vword[m] + kk) << 3));
   }
   float *table = reinterpret_cast<float *>(table_p);
   const float *kcb = c_cb[KB - 2], *vcb = c_cb[VB - 2];
@@ -233,16 +272,27 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 
   int stage = 0;
   uint32_t phase = 0;
+#ifdef AQ_PROBE
+  unsigned long long probe_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long probe_last = clock64();
+  int probe_phase = 5;
+#endif
   auto wait_full = [&]() {
+#ifdef AQ_PROBE
+    const long long w0__ = clock64();
+#endif
     if (*reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(&full[stage], phase)) {
       *reinterpret_cast<volatile int *>(s_fail) = 1;
       atomicExch(a.status, 1);
     }
+#ifdef AQ_PROBE
+    if (tid == 0) probe_acc[probe_phase] += (unsigned long long)(clock64() - w0__);
+#endif
   };
   auto release = [&]() {
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[stage]);
-    if (++stage == CS_STAGES) { stage = 0; phase ^= 1u; }
+    if (++stage == n_stages) { stage = 0; phase ^= 1u; }
   };
 
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -253,6 +303,11 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     const int len = t1 - t0;
     const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
     const float *q = a.q + (size_t)hq * dim;
+    { // pull this span's K and V scale lines into L2; they are read after the K stream
+      const float *sp = (tid < 256 ? c.k_scale : c.v_scale) + (size_t)h * c.s_stride + t0;
+      const int off = (tid & 255) * 32; // floats; 128-byte lines
+      if (off < len) asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + off));
+    }
 
     // ---- rotate the query (attention.cpp:537-550) -------------------------
     if (tid < P) qr[tid] = tid < dim ? q[tid] : 0.f;
@@ -264,7 +319,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     consumer_butterflies(qr, P);
     if (tid < P) qr[tid] = qr[tid] * isp * (sqrtf((float)P) * qn);
     // ---- zero the buckets, build the K byte table ---------------------------
-    for (int i = tid; i < CS_TABLE_BYTES / 4; i += CS_CONSUMERS) bucket[i] = 0u;
+    for (int i = tid; i < BUCKET_BYTES / 4; i += CS_CONSUMERS) bucket[i] = 0u;
     consumer_sync();
     {
       // thread -> column (consecutive lanes, consecutive banks), a slice of the byte values
@@ -300,12 +355,14 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     }
     consumer_sync();
 
+    AQ_MARK(0)
+#ifdef AQ_PROBE
+    probe_phase = 5;
+#endif
     // ---- K stream: raw dot products into sc[] ---------------------------------------
     for (int t = t0; t < t1; t += TKN) {
       wait_full();
-      const uint32_t st_addr = smem_u32(ring + (size_t)stage * CS_STAGE_BYTES);
-      const uint32_t *stw = reinterpret_cast<const uint32_t *>(ring + (size_t)stage * CS_STAGE_BYTES);
-      (void)st_addr;
+      const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
       uint32_t dk[KSTEPS][KWPL];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
@@ -335,42 +392,59 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     }
     consumer_sync();
 
+    AQ_MARK(1)
     // ---- exact two-pass softmax over the span ------------------------------------------
+    // Each thread owns tokens tid, tid+512, ...; their scales are fetched in one
+    // batch (the lines were pulled into L2 at the start of the item) and every
+    // intermediate stays in registers.
+    constexpr int NPT = CS_SPAN_MAX / CS_CONSUMERS;
     const float *ksc = c.k_scale + (size_t)h * c.s_stride + t0;
     const float *vsc = c.v_scale + (size_t)h * c.s_stride + t0;
+    float sv[NPT], vv[NPT];
+#pragma unroll
+    for (int r = 0; r < NPT; ++r) {
+      const int i = tid + r * CS_CONSUMERS;
+      sv[r] = i < len ? __ldg(ksc + i) : 0.f;
+      vv[r] = i < len ? __ldg(vsc + i) : 0.f;
+    }
     float mx = -INFINITY;
-    for (int i = tid; i < len; i += CS_CONSUMERS) {
-      const float s = sc[i] * attn_s * ksc[i];
-      sc[i] = s;
-      mx = fmaxf(mx, s);
+#pragma unroll
+    for (int r = 0; r < NPT; ++r) {
+      const int i = tid + r * CS_CONSUMERS;
+      sv[r] = i < len ? sc[i] * attn_s * sv[r] : -INFINITY;
+      mx = fmaxf(mx, sv[r]);
     }
     mx = consumer_reduce(mx, red, true);
     float ls = 0.f, wsum = 0.f;
-    const int len_pad = min(CS_SPAN_MAX, (len + TVN - 1) / TVN * TVN);
-    for (int i = tid; i < len_pad; i += CS_CONSUMERS) {
-      float w = 0.f;
-      if (i < len) {
-        const float e = expf(sc[i] - mx);
-        ls += e;
-        w = e * vsc[i] * isp;
-        wsum += w;
-      }
-      sc[i] = w;
+#pragma unroll
+    for (int r = 0; r < NPT; ++r) {
+      const float e = expf(sv[r] - mx); // exp(-inf) = 0 for the padding
+      ls += e;
+      sv[r] = e * vv[r] * isp;
+      wsum += sv[r];
     }
-    ls = consumer_reduce(ls, red, false);
-    wsum = consumer_reduce(wsum, red, false);
+    consumer_reduce2(ls, wsum, red);
     // weights -> 32-bit fixed point with the span's total mapped to 2^30, so no
     // bucket can overflow and the rounding error is below 2^-31 of the total per token
     const float fx = (wsum > 0.f && wsum < INFINITY) ? 1073741824.0f / wsum : 0.f;
     const float inv_fx = fx > 0.f ? wsum * (1.0f / 1073741824.0f) : 0.f;
     uint32_t *scu = reinterpret_cast<uint32_t *>(sc);
-    for (int i = tid; i < len_pad; i += CS_CONSUMERS) scu[i] = __float2uint_rn(sc[i] * fx);
+    const int len_pad = min(CS_SPAN_MAX, (len + TVN - 1) / TVN * TVN);
+#pragma unroll
+    for (int r = 0; r < NPT; ++r) {
+      const int i = tid + r * CS_CONSUMERS;
+      if (i < len_pad) scu[i] = __float2uint_rn(sv[r] * fx);
+    }
     consumer_sync();
 
+    AQ_MARK(2)
+#ifdef AQ_PROBE
+    probe_phase = 6;
+#endif
     // ---- V stream: add each token's weight into bucket[byte][column] ---------------------
     for (int t = t0; t < t1; t += TVN) {
       wait_full();
-      const uint32_t *stw = reinterpret_cast<const uint32_t *>(ring + (size_t)stage * CS_STAGE_BYTES);
+      const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
       uint32_t dv[VSTEPS][VWPL], wv[VSTEPS];
 #pragma unroll
       for (int s = 0; s < VSTEPS; ++s) {
@@ -384,35 +458,43 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
         for (int m = 0; m < VWPL; ++m) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) red_shared_add(__byte_perm(dv[s][m], vconst[m][k], ksel[k]), wv[s]);
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t ad = __byte_perm(dv[s][m], vconst[m][k], ksel[k]);
+            red_shared_add(VC == 64 ? ad : (ad >> 1), wv[s]);
+          }
         }
       }
       release();
     }
     consumer_sync();
 
+    AQ_MARK(3)
     // ---- buckets -> rotated-domain accumulator -------------------------------------------
-    // acc[j] = sum over byte values of bucket[byte][column(j)] * centroid[digit_j(byte)]
+    // acc[j] = sum over byte values of bucket[byte][column(j)] * centroid[digit_j(byte)].
+    // A thread owns one byte column and a slice of the 256 byte values, reads each
+    // bucket once and feeds the VE coordinates packed in that byte.
     {
-      constexpr int PARTS = CS_CONSUMERS / P; // 2 (P=128) or 4 (P=64)
-      const int j = tid % P, part = tid / P;
-      const int col = j / VE, e = j % VE;
-      const int shift = 8 - VB * (e + 1);
-      float av = 0.f;
-      for (int b = part; b < 256; b += PARTS) {
-        uint32_t bi = bucket[b * 64 + col];
-        if (VC == 32) bi += bucket[b * 64 + 32 + col];
-        av += (float)bi * vcb[(b >> shift) & ((1 << VB) - 1)];
+      constexpr int NPARTS = CS_CONSUMERS / VC, BPP = 256 / NPARTS;
+      const int col = tid % VC, part = tid / VC; // a warp shares `part`, so centroid reads broadcast
+      float av[VE];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) av[e] = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < BPP; ++i) {
+        const int b = part * BPP + i;
+        const float bv = (float)bucket[b * VC + col];
+#pragma unroll
+        for (int e = 0; e < VE; ++e) av[e] += bv * s_cb[(b >> (8 - VB * (e + 1))) & ((1 << VB) - 1)];
       }
-      av *= inv_fx;
       consumer_sync(); // all bucket reads done before sc[] is reused as fold space
-      sc[tid] = av;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) sc[part * P + col * VE + e] = av[e] * inv_fx;
       consumer_sync();
       if (tid < P) {
-        float s = 0.f;
+        float t = 0.f;
 #pragma unroll
-        for (int g = 0; g < PARTS; ++g) s += sc[g * P + tid];
-        qr[tid] = s; // qr is free now
+        for (int g = 0; g < NPARTS; ++g) t += sc[g * P + tid];
+        qr[tid] = t; // qr is free now
       }
       consumer_sync();
     }
@@ -427,7 +509,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       if (tid < dim) a.out[(size_t)hq * dim + tid] = qr[tid] * isp * sign_of(sg, tid);
     }
     consumer_sync();
+    AQ_MARK(4)
   }
+#ifdef AQ_PROBE
+  if (tid == 0 && a.probe)
+    for (int k = 0; k < 7; ++k) atomicAdd(a.probe + k, probe_acc[k]);
+#endif
 }
 
 } // namespace aq

@@ -1006,6 +1006,111 @@ int adaptq_mha_export_head(adaptq_mha_t h, int head_idx, uint8_t *k_rows, uint8_
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// adaptq_mha_compute_all_static: decode attention that allocates nothing.
+//
+// Some callers cannot let a library touch the device allocator once they are
+// running: a serving engine that has handed every free byte of HBM to its own
+// pool (a late cudaMalloc simply fails there), or a latency-critical decode
+// loop that cannot tolerate the device-wide synchronisation an allocation or
+// free may imply.  For them the split-KV partials go into a fixed array that
+// is part of the library image instead of a lazily grown cudaMalloc buffer.
+//
+// The array is a file-scope __device__ object: every GPU that loads the
+// library holds AQ_STATIC_SCRATCH_BYTES of it until the process exits.  In
+// host code its name is only a handle, not a device address, so the address
+// is looked up with cudaGetSymbolAddress -- once per device, by the first
+// call made while that device is current.
+// ---------------------------------------------------------------------------
+#define AQ_STATIC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) float g_static_partials[AQ_STATIC_SCRATCH_BYTES / sizeof(float)];
+static float *g_static_partials_addr[64] = {};
+static std::mutex g_static_mu;
+
+int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int queries_per_head, float *outs) {
+  MHA_PROLOGUE("adaptq_mha_compute_all_static", -1)
+  if (queries_per_head <= 0) { set_error("adaptq_mha_compute_all_static: queries_per_head must be positive"); return -1; }
+  if (!require_pointer(queries, "adaptq_mha_compute_all_static", "queries") ||
+      !require_pointer(outs, "adaptq_mha_compute_all_static", "outs"))
+    return -1;
+  clear_error();
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  const CacheView &c = g->c;
+  if (ptr_kind(queries) != PK_DEVICE || ptr_kind(outs) != PK_DEVICE) {
+    set_error("adaptq_mha_compute_all_static: queries and outs must be device memory (staging host buffers would allocate)");
+    return -1;
+  }
+  if (!stream_supported(c) || c.v_mass > 0.f || c.hyb > 0 || g->device < 0 || g->device >= 64) {
+    set_error("adaptq_mha_compute_all_static: needs 2/4-bit K and V at head dim 64/128 (4-bit only at 64), dense V, no hybrid window");
+    return -1;
+  }
+  if (!g->uniform) {
+    set_error("adaptq_mha_compute_all_static: heads hold different token counts; use adaptq_mha_compute_all");
+    return -1;
+  }
+  const int n = g->u.size;
+  const int items_base = c.n_heads * queries_per_head;
+  if (n == 0) {
+    cudaError_t e = cudaMemsetAsync(outs, 0, (size_t)items_base * c.dim * sizeof(float), g->stream);
+    if (e != cudaSuccess) { set_error("adaptq_mha_compute_all_static: CUDA error: %s", cudaGetErrorString(e)); return -1; }
+    return 0;
+  }
+  // device address of the static scratch, once per device (this device is current)
+  float *scratch;
+  {
+    std::lock_guard<std::mutex> sl(g_static_mu);
+    if (!g_static_partials_addr[g->device]) {
+      void *p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_static_partials);
+      if (e != cudaSuccess || !p) {
+        set_error("adaptq_mha_compute_all_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        return -1;
+      }
+      g_static_partials_addr[g->device] = static_cast<float *>(p);
+    }
+    scratch = g_static_partials_addr[g->device];
+  }
+  StreamLaunch a{};
+  a.c = c; a.q = queries; a.out = outs; a.head0 = 0; a.heads_in_call = c.n_heads; a.nq = queries_per_head;
+  a.n = n; a.status = g->d_status;
+  plan_spans(n, items_base, g->sm_count, a.n_splits, a.span);
+  const size_t need = (size_t)a.n_splits * items_base * partial_floats(c) * sizeof(float);
+  if (a.n_splits > 1 && need > AQ_STATIC_SCRATCH_BYTES) {
+    set_error("adaptq_mha_compute_all_static: %zu bytes of split-KV partials exceed the %u-byte static scratch "
+              "(fewer heads or queries per call, or use adaptq_mha_compute_all)", need, (unsigned)AQ_STATIC_SCRATCH_BYTES);
+    return -1;
+  }
+  // Every (span, head, query) slot that the merge reads is written by the
+  // streaming kernel first, so nothing in the array has to start at zero.
+  a.partial = scratch;
+  a.force_partial = 0;
+#ifdef AQ_PROBE
+  a.probe = nullptr;
+#endif
+  const long long items = (long long)items_base * a.n_splits;
+  const int grid = (int)std::min<long long>(items, g->sm_count);
+  bool ok;
+  if (c.padded == 128) {
+    if (c.k_bits == 4 && c.v_bits == 2) ok = launch_stream_t<4, 16, 2, 8>(g, a, grid);
+    else if (c.k_bits == 4 && c.v_bits == 4) ok = launch_stream_t<4, 16, 4, 16>(g, a, grid);
+    else if (c.k_bits == 2 && c.v_bits == 2) ok = launch_stream_t<2, 8, 2, 8>(g, a, grid);
+    else ok = launch_stream_t<2, 8, 4, 16>(g, a, grid);
+  } else {
+    ok = launch_stream_t<4, 8, 4, 8>(g, a, grid);
+  }
+  if (!ok) return -1;
+  if (a.n_splits > 1) {
+    merge_partials_kernel<<<items_base, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
+        scratch, (size_t)items_base * partial_floats(c), a.n_splits, c, 0, queries_per_head, outs, 0, 0);
+    ++g_launches;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("adaptq_mha_compute_all_static: CUDA error: %s", cudaGetErrorString(e)); return -1; }
+  }
+  return n;
+}
+
+
 #ifdef AQ_PROBE
 int adaptq_probe_read(unsigned long long *out, int reset) {
   if (!g_probe) return -1;

@@ -60,6 +60,34 @@ int adaptq_mha_compute_partial(adaptq_mha_t mha, const float *queries,
 int adaptq_mha_merge_partials(adaptq_mha_t mha, const float *partials,
                               int n_parts, int queries_per_head, float *outs);
 
+/* Decode attention for every head WITHOUT any device or host allocation.
+ * This entry point has no counterpart in upstream; it exists for callers
+ * that must not reach the CUDA allocator after start-up -- an inference
+ * server whose memory pool already owns all free HBM (a late cudaMalloc
+ * fails there), or a decode loop that cannot afford the device-wide stall
+ * an allocation or free can cause.  Same result as adaptq_mha_compute_all.
+ *
+ *  - queries, outs: DEVICE memory, float [n_heads][queries_per_head][dim].
+ *  - Shapes of the streaming kernel only: K and V at 2 or 4 bits with head
+ *    dim 128 (4/4 bits at dim 64), v_mass <= 0, hybrid_thresh == 0, all heads
+ *    holding the same number of tokens.  Anything else returns -1.
+ *  - The split-KV partials live in a 4 MiB array inside the library image
+ *    (held on every GPU that loads the library, until the process exits)
+ *    instead of a cudaMalloc buffer.  A call needing more -- spans x n_heads
+ *    x queries_per_head x (2 + padded) floats -- is refused with -1 and an
+ *    error text; nothing is truncated.
+ *  - The first call made on a device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call outside any stream
+ *    capture.  Later calls do no set-up.
+ *  - All handles and all calls on a device share the one array and it keeps
+ *    the previous call's contents.  Nothing in it needs clearing (every slot
+ *    read is written first by the same call), but two such calls that
+ *    overlap on the GPU -- different streams or handles -- race on it:
+ *    serialise them.
+ * Returns the token count, or -1 with adaptq_last_error() set. */
+int adaptq_mha_compute_all_static(adaptq_mha_t mha, const float *queries,
+                                  int queries_per_head, float *outs);
+
 /* Use `cuda_stream` (a cudaStream_t; NULL = the default stream) for all
  * further work of this handle. */
 int adaptq_mha_set_stream(adaptq_mha_t mha, void *cuda_stream);

@@ -121,6 +121,33 @@ __device__ __forceinline__ void consumer_butterflies(float *x, int p) {
   }
 }
 
+// Walsh-Hadamard butterflies over P = 32*EPL values held EPL per lane (lane l
+// owns elements EPL*l .. EPL*l+EPL-1), stage order len = 1, 2, ... P/2, lower
+// index a+b, upper a-b (core/fwht.cpp:36-57).  One warp, no shared memory.
+template <int EPL> __device__ __forceinline__ void warp_butterflies(float (&v)[EPL], int lane) {
+#pragma unroll
+  for (int len = 1; len < EPL; len <<= 1) {
+#pragma unroll
+    for (int i = 0; i < EPL; i += (len << 1)) {
+#pragma unroll
+      for (int j = 0; j < len; ++j) {
+        const float a = v[i + j], b = v[i + j + len];
+        v[i + j] = a + b;
+        v[i + j + len] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
+      v[e] = upper ? other - v[e] : v[e] + other;
+    }
+  }
+}
+
 // Sum STEPS per-lane partials across the 8 lanes of a token group so that
 // each lane ends with complete sums; returns the value this lane owns and the
 // step it belongs to (8 steps: lane wl owns step wl; 4 steps: lanes wl, wl^1
@@ -295,6 +322,13 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     if (++stage == n_stages) { stage = 0; phase ^= 1u; }
   };
 
+  constexpr int EPL = P / 32; // query / accumulator elements per lane of warp 0
+  float q_next[EPL];
+  if (warp == 0 && (int)blockIdx.x < n_items) {
+    const float *q0 = a.q + (size_t)(blockIdx.x / a.n_splits) * dim;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) q_next[e] = (EPL * lane + e) < dim ? __ldg(q0 + EPL * lane + e) : 0.f;
+  }
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int split = item % a.n_splits, hq = item / a.n_splits;
     const int hl = hq / a.nq;
@@ -302,25 +336,43 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     const int t0 = min(a.n, split * a.span), t1 = min(a.n, t0 + a.span);
     const int len = t1 - t0;
     const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
-    const float *q = a.q + (size_t)hq * dim;
     { // pull this span's K and V scale lines into L2; they are read after the K stream
       const float *sp = (tid < 256 ? c.k_scale : c.v_scale) + (size_t)h * c.s_stride + t0;
       const int off = (tid & 255) * 32; // floats; 128-byte lines
       if (off < len) asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + off));
     }
 
-    // ---- rotate the query (attention.cpp:537-550) -------------------------
-    if (tid < P) qr[tid] = tid < dim ? q[tid] : 0.f;
+    // ---- rotate the query (attention.cpp:537-550): warp 0, in registers; the other
+    // warps clear the buckets meanwhile ------------------------------------------------
+    if (warp == 0) {
+      float v[EPL];
+      float part = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        v[e] = q_next[e];
+        part += v[e] * v[e];
+      }
+      { // fetch the next item's query now; it is consumed one iteration later
+        const int nitem = item + gridDim.x;
+        if (nitem < n_items) {
+          const float *qn_ptr = a.q + (size_t)(nitem / a.n_splits) * dim;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) q_next[e] = (EPL * lane + e) < dim ? __ldg(qn_ptr + EPL * lane + e) : 0.f;
+        }
+      }
+      const float qn = sqrtf(warp_sum(part) + 1e-12f);
+      const float inv = 1.f / qn;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[e] = v[e] * inv * sign_of(sg, EPL * lane + e);
+      warp_butterflies<EPL>(v, lane);
+      const float back = sqrtf((float)P) * qn;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) qr[EPL * lane + e] = v[e] * isp * back;
+    } else {
+      for (int i = tid - 32; i < BUCKET_BYTES / 4; i += CS_CONSUMERS - 32) bucket[i] = 0u;
+    }
     consumer_sync();
-    float part = (tid < dim) ? qr[tid] * qr[tid] : 0.f;
-    const float qn = sqrtf(consumer_reduce(part, red, false) + 1e-12f);
-    if (tid < P) qr[tid] = qr[tid] * (1.f / qn) * sign_of(sg, tid);
-    consumer_sync();
-    consumer_butterflies(qr, P);
-    if (tid < P) qr[tid] = qr[tid] * isp * (sqrtf((float)P) * qn);
-    // ---- zero the buckets, build the K byte table ---------------------------
-    for (int i = tid; i < BUCKET_BYTES / 4; i += CS_CONSUMERS) bucket[i] = 0u;
-    consumer_sync();
+    // ---- build the K byte table ----------------------------------------------------
     {
       // thread -> column (consecutive lanes, consecutive banks), a slice of the byte values
       constexpr int HPT = 16 / (CS_CONSUMERS / 64); // high-nibble values per thread
@@ -390,12 +442,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       if ((KSTEPS == 8 || (wl & 1) == 0) && t + tok < t1) sc[t - t0 + tok] = total;
       release();
     }
-    consumer_sync();
-
-    AQ_MARK(1)
     // ---- exact two-pass softmax over the span ------------------------------------------
     // Each thread owns tokens tid, tid+512, ...; their scales are fetched in one
-    // batch (the lines were pulled into L2 at the start of the item) and every
+    // batch (the lines were pulled into L2 at the start of the item; the loads
+    // are issued before the barrier so their latency overlaps the wait) and every
     // intermediate stays in registers.
     constexpr int NPT = CS_SPAN_MAX / CS_CONSUMERS;
     const float *ksc = c.k_scale + (size_t)h * c.s_stride + t0;
@@ -407,6 +457,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       sv[r] = i < len ? __ldg(ksc + i) : 0.f;
       vv[r] = i < len ? __ldg(vsc + i) : 0.f;
     }
+    consumer_sync();
+    AQ_MARK(1)
     float mx = -INFINITY;
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
@@ -502,11 +554,17 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       float *pp = a.partial + ((size_t)split * items_base + hq) * (size_t)(2 + P);
       if (tid == 0) { pp[0] = mx; pp[1] = ls; }
       if (tid < P) pp[2 + tid] = qr[tid];
-    } else {
-      if (tid < P) qr[tid] *= (1.f / ls);
-      consumer_sync();
-      consumer_butterflies(qr, P);
-      if (tid < dim) a.out[(size_t)hq * dim + tid] = qr[tid] * isp * sign_of(sg, tid);
+    } else if (warp == 0) { // normalise, inverse transform (core/fwht.cpp:106-134), write
+      float v[EPL];
+      const float invl = 1.f / ls;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[e] = qr[EPL * lane + e] * invl;
+      warp_butterflies<EPL>(v, lane);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const int j = EPL * lane + e;
+        if (j < dim) a.out[(size_t)hq * dim + j] = v[e] * isp * sign_of(sg, j);
+      }
     }
     consumer_sync();
     AQ_MARK(4)

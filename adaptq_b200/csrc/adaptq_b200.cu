@@ -531,7 +531,7 @@ bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, flo
   a.c = c; a.q = ca.q; a.out = ca.out; a.head0 = ca.head0; a.heads_in_call = ca.heads_in_call; a.nq = ca.nq;
   a.n = ca.n; a.status = g->d_status;
 #ifdef AQ_PROBE
-  if (!g_probe) { cudaMalloc(&g_probe, 64); cudaMemset(g_probe, 0, 64); }
+  if (!g_probe) { cudaMalloc(&g_probe, 256); cudaMemset(g_probe, 0, 256); }
   a.probe = g_probe;
 #endif
   const int items_base = a.heads_in_call * a.nq;
@@ -1115,8 +1115,8 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
 int adaptq_probe_read(unsigned long long *out, int reset) {
   if (!g_probe) return -1;
   cudaDeviceSynchronize();
-  cudaMemcpy(out, g_probe, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-  if (reset) cudaMemset(g_probe, 0, 8 * sizeof(unsigned long long));
+  cudaMemcpy(out, g_probe, 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  if (reset) cudaMemset(g_probe, 0, 32 * sizeof(unsigned long long));
   return 0;
 }
 #endif

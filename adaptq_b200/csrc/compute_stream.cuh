@@ -301,19 +301,38 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   uint32_t phase = 0;
 #ifdef AQ_PROBE
   unsigned long long probe_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  unsigned long long probe_mywait = 0;
+  unsigned long long probe_hist[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   long long probe_last = clock64();
   int probe_phase = 5;
 #endif
+  bool next_ready = false;
+  // Poll the barrier of the stage after the current one without blocking; the
+  // answer is used by the next wait_full(), so the poll's latency (it queues
+  // behind the table reads) overlaps this tile's arithmetic.
+  auto peek_next = [&]() {
+    const int ns = stage + 1 == n_stages ? 0 : stage + 1;
+    const uint32_t np = stage + 1 == n_stages ? phase ^ 1u : phase;
+    next_ready = mbar_test(&full[ns], np);
+  };
   auto wait_full = [&]() {
 #ifdef AQ_PROBE
     const long long w0__ = clock64();
 #endif
-    if (*reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(&full[stage], phase)) {
+    // The stage was already tested (peek_next) while the previous tile was being
+    // processed; only a stage that had not landed by then is waited for here.
+    if (!next_ready && *reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(&full[stage], phase)) {
       *reinterpret_cast<volatile int *>(s_fail) = 1;
       atomicExch(a.status, 1);
     }
 #ifdef AQ_PROBE
-    if (tid == 0) probe_acc[probe_phase] += (unsigned long long)(clock64() - w0__);
+    if (tid == 0) {
+      const unsigned long long dt__ = (unsigned long long)(clock64() - w0__);
+      probe_acc[probe_phase] += dt__;
+      const int bin__ = dt__ < 100 ? 0 : dt__ < 500 ? 1 : dt__ < 2000 ? 2 : 3;
+      probe_hist[bin__] += 1; probe_hist[4 + bin__] += dt__;
+    }
+    probe_mywait += (unsigned long long)(clock64() - w0__);
 #endif
   };
   auto release = [&]() {
@@ -422,6 +441,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
         for (int m = 0; m < KWPL; ++m) dk[s][m] = stw[tok * KW + kword[m]];
       }
+      peek_next();
       float pv[KSTEPS];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
@@ -505,6 +525,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
         for (int m = 0; m < VWPL; ++m) dv[s][m] = stw[tok * VW + vword[m]];
       }
+      peek_next();
 #pragma unroll
       for (int s = 0; s < VSTEPS; ++s) {
 #pragma unroll
@@ -572,6 +593,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #ifdef AQ_PROBE
   if (tid == 0 && a.probe)
     for (int k = 0; k < 7; ++k) atomicAdd(a.probe + k, probe_acc[k]);
+  if (lane == 0 && a.probe) atomicAdd(a.probe + 8 + warp, probe_mywait);
+  if (tid == 0 && a.probe)
+    for (int k = 0; k < 8; ++k) atomicAdd(a.probe + 24 + k, probe_hist[k]);
 #endif
 }
 

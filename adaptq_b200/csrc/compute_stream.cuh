@@ -34,6 +34,13 @@
 #pragma once
 #include "common.cuh"
 
+#ifndef AQ_COMPACT_BUCKETS
+#define AQ_COMPACT_BUCKETS 1
+#endif
+#ifndef AQ_PACKED_ADD
+#define AQ_PACKED_ADD 1
+#endif
+
 namespace aq {
 
 #ifdef AQ_PROBE
@@ -188,7 +195,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   constexpr int KWPL = KW / 8, VWPL = VW / 8;                               // words per lane
   constexpr int KC = KW * 4, VC = VW * 4;                                   // byte columns
   constexpr int KE = 8 / KB, VE = 8 / VB;                                   // coordinates per byte
-  constexpr int BUCKET_BYTES = VC * 1024;                                   // [256][VC] 32-bit buckets
+  constexpr bool COMPACT = AQ_COMPACT_BUCKETS && VC == 32;
+  constexpr int BUCKET_BYTES = COMPACT ? 32768 : CS_TABLE_BYTES;           // [256][32 or 64] 32-bit buckets
 
   extern __shared__ __align__(1024) unsigned char smem_stream[];
   unsigned char *smem = smem_stream;
@@ -279,6 +287,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   for (int m = 0; m < KWPL; ++m) kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
 #pragma unroll
   for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+  // With 32 byte columns (2-bit V at dim 128, 4-bit at dim 64) the 64-column rows
+  // hold two copies of the buckets; the upper half of the warps uses the second.
+  const int vcol_off = (VC == 32 && !COMPACT && warp >= CS_WARPS / 2) ? 32 : 0;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int kk = (k + tq) & 3;
@@ -286,14 +297,14 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
     for (int m = 0; m < KWPL; ++m) kconst[m][k] = table_addr | (uint32_t)((4 * kword[m] + kk) << 2);
 #pragma unroll
-    // bucket rows are VC*4 bytes: with 64 columns the byte lands in address bits
-    // 8..15 directly; with 32 columns the address is formed doubled and halved after
+    // bucket rows are 64 columns (256 bytes), so the packed byte lands in address
+    // bits 8..15 with one byte-permute
     for (int m = 0; m < VWPL; ++m)
-      vconst[m][k] = VC == 64 ? (bucket_addr | (uint32_t)((4 * vword[m] + kk) << 2))
-                              : ((bucket_addr << 1) | (uint32_t)((4 * vword[m] + kk) << 3));
+      vconst[m][k] = COMPACT ? ((bucket_addr << 1) | (uint32_t)((4 * vword[m] + kk) << 3))
+                             : (bucket_addr | (uint32_t)((4 * vword[m] + kk + vcol_off) << 2));
   }
   float *table = reinterpret_cast<float *>(table_p);
-  const float *kcb = c_cb[KB - 2], *vcb = c_cb[VB - 2];
+  const float *kcb = c_cb[KB - 2];
   const float isp = 1.f / sqrtf((float)P);
   const float attn_s = 1.f / (sqrtf((float)dim) * (float)P);
 
@@ -343,18 +354,21 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 
   constexpr int EPL = P / 32; // query / accumulator elements per lane of warp 0
   float q_next[EPL];
+  uint32_t sg_next = 0; // the sign word covering this lane's elements (EPL divides 32)
   if (warp == 0 && (int)blockIdx.x < n_items) {
-    const float *q0 = a.q + (size_t)(blockIdx.x / a.n_splits) * dim;
+    const int hq0 = blockIdx.x / a.n_splits;
+    const float *q0 = a.q + (size_t)hq0 * dim;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) q_next[e] = (EPL * lane + e) < dim ? __ldg(q0 + EPL * lane + e) : 0.f;
+    sg_next = __ldg(c.signs + (size_t)(a.head0 + hq0 / a.nq) * c.sign_words + ((EPL * lane) >> 5));
   }
+  uint32_t sg_cur = 0;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int split = item % a.n_splits, hq = item / a.n_splits;
     const int hl = hq / a.nq;
     const int h = a.head0 + hl;
     const int t0 = min(a.n, split * a.span), t1 = min(a.n, t0 + a.span);
     const int len = t1 - t0;
-    const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
     { // pull this span's K and V scale lines into L2; they are read after the K stream
       const float *sp = (tid < 256 ? c.k_scale : c.v_scale) + (size_t)h * c.s_stride + t0;
       const int off = (tid & 255) * 32; // floats; 128-byte lines
@@ -371,18 +385,21 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         v[e] = q_next[e];
         part += v[e] * v[e];
       }
-      { // fetch the next item's query now; it is consumed one iteration later
+      sg_cur = sg_next;
+      { // fetch the next item's query and signs now; they are consumed one iteration later
         const int nitem = item + gridDim.x;
         if (nitem < n_items) {
-          const float *qn_ptr = a.q + (size_t)(nitem / a.n_splits) * dim;
+          const int nhq = nitem / a.n_splits;
+          const float *qn_ptr = a.q + (size_t)nhq * dim;
 #pragma unroll
           for (int e = 0; e < EPL; ++e) q_next[e] = (EPL * lane + e) < dim ? __ldg(qn_ptr + EPL * lane + e) : 0.f;
+          sg_next = __ldg(c.signs + (size_t)(a.head0 + nhq / a.nq) * c.sign_words + ((EPL * lane) >> 5));
         }
       }
       const float qn = sqrtf(warp_sum(part) + 1e-12f);
       const float inv = 1.f / qn;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) v[e] = v[e] * inv * sign_of(sg, EPL * lane + e);
+      for (int e = 0; e < EPL; ++e) v[e] = v[e] * inv * (((sg_cur >> ((EPL * lane + e) & 31)) & 1u) ? -1.f : 1.f);
       warp_butterflies<EPL>(v, lane);
       const float back = sqrtf((float)P) * qn;
 #pragma unroll
@@ -430,10 +447,20 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #ifdef AQ_PROBE
     probe_phase = 5;
 #endif
-    // ---- K stream: raw dot products into sc[] ---------------------------------------
+    // ---- K stream: logits into sc[] ----------------------------------------------------
+    // After the group reduction one lane per token owns its dot product; that lane
+    // also fetches the token's K scale (early, so the load overlaps the tile) and
+    // keeps a running maximum, so no separate scaling pass is needed.
+    const float *ksc = c.k_scale + (size_t)h * c.s_stride + t0;
+    const float *vsc = c.v_scale + (size_t)h * c.s_stride + t0;
+    const int own_tok = warp * (TKN / CS_WARPS) + 4 * (KSTEPS == 8 ? wl : (wl >> 1)) + tq;
+    const bool owner = KSTEPS == 8 || (wl & 1) == 0;
+    float lane_max = -INFINITY;
     for (int t = t0; t < t1; t += TKN) {
       wait_full();
       const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
+      const bool own_valid = owner && t + own_tok < t1;
+      const float ksv = own_valid ? __ldg(ksc + (t - t0) + own_tok) : 0.f;
       uint32_t dk[KSTEPS][KWPL];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
@@ -445,6 +472,23 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       float pv[KSTEPS];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
+#if AQ_PACKED_ADD
+        unsigned long long acc2 = 0ull; // two running sums, added with one f32x2 instruction
+#pragma unroll
+        for (int m = 0; m < KWPL; ++m) {
+          const uint32_t d = dk[s][m];
+#pragma unroll
+          for (int k = 0; k < 4; k += 2) {
+            const float e0 = lds_f32(__byte_perm(d, kconst[m][k], ksel[k]));
+            const float e1 = lds_f32(__byte_perm(d, kconst[m][k + 1], ksel[k + 1]));
+            unsigned long long e2;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(e2) : "f"(e0), "f"(e1));
+            asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc2) : "l"(e2));
+          }
+        }
+        float a0, a1;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc2));
+#else
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
         for (int m = 0; m < KWPL; ++m) {
@@ -454,12 +498,15 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
           a0 += lds_f32(__byte_perm(d, kconst[m][2], ksel[2]));
           a1 += lds_f32(__byte_perm(d, kconst[m][3], ksel[3]));
         }
+#endif
         pv[s] = a0 + a1;
       }
       const float total = group_transpose_sum<KSTEPS>(pv, wl);
-      const int step = KSTEPS == 8 ? wl : (wl >> 1);
-      const int tok = warp * (TKN / CS_WARPS) + 4 * step + tq;
-      if ((KSTEPS == 8 || (wl & 1) == 0) && t + tok < t1) sc[t - t0 + tok] = total;
+      if (own_valid) {
+        const float logit = total * attn_s * ksv;
+        sc[t - t0 + own_tok] = logit;
+        lane_max = fmaxf(lane_max, logit);
+      }
       release();
     }
     // ---- exact two-pass softmax over the span ------------------------------------------
@@ -468,25 +515,19 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // are issued before the barrier so their latency overlaps the wait) and every
     // intermediate stays in registers.
     constexpr int NPT = CS_SPAN_MAX / CS_CONSUMERS;
-    const float *ksc = c.k_scale + (size_t)h * c.s_stride + t0;
-    const float *vsc = c.v_scale + (size_t)h * c.s_stride + t0;
     float sv[NPT], vv[NPT];
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
       const int i = tid + r * CS_CONSUMERS;
-      sv[r] = i < len ? __ldg(ksc + i) : 0.f;
       vv[r] = i < len ? __ldg(vsc + i) : 0.f;
     }
-    consumer_sync();
     AQ_MARK(1)
-    float mx = -INFINITY;
+    const float mx = consumer_reduce(lane_max, red, true); // its barriers also publish sc[]
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
       const int i = tid + r * CS_CONSUMERS;
-      sv[r] = i < len ? sc[i] * attn_s * sv[r] : -INFINITY;
-      mx = fmaxf(mx, sv[r]);
+      sv[r] = i < len ? sc[i] : -INFINITY;
     }
-    mx = consumer_reduce(mx, red, true);
     float ls = 0.f, wsum = 0.f;
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
@@ -533,7 +574,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t ad = __byte_perm(dv[s][m], vconst[m][k], ksel[k]);
-            red_shared_add(VC == 64 ? ad : (ad >> 1), wv[s]);
+            red_shared_add(COMPACT ? (ad >> 1) : ad, wv[s]);
           }
         }
       }
@@ -555,7 +596,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll 8
       for (int i = 0; i < BPP; ++i) {
         const int b = part * BPP + i;
-        const float bv = (float)bucket[b * VC + col];
+        uint32_t bi = COMPACT ? bucket[b * 32 + col] : bucket[b * 64 + col];
+        if (VC == 32 && !COMPACT) bi += bucket[b * 64 + 32 + col];
+        const float bv = (float)bi;
 #pragma unroll
         for (int e = 0; e < VE; ++e) av[e] += bv * s_cb[(b >> (8 - VB * (e + 1))) & ((1 << VB) - 1)];
       }
@@ -584,7 +627,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
       for (int e = 0; e < EPL; ++e) {
         const int j = EPL * lane + e;
-        if (j < dim) a.out[(size_t)hq * dim + j] = v[e] * isp * sign_of(sg, j);
+        if (j < dim) a.out[(size_t)hq * dim + j] = v[e] * isp * (((sg_cur >> (j & 31)) & 1u) ? -1.f : 1.f);
       }
     }
     consumer_sync();

@@ -303,19 +303,17 @@ bool check_status(Group *g, const char *fn) {
 // ---------------------------------------------------------------------------
 template <int P, int BITS>
 bool launch_rows(Group *g, const AppendLaunch &a) {
-  constexpr int THREADS = 128;
-  constexpr size_t SMEM = ((size_t)THREADS * (P + 4) + (size_t)(THREADS / 32) * P) * sizeof(float);
+  constexpr size_t SMEM = ((size_t)AT_TILE * (P + 4) + (size_t)(AT_THREADS / 32) * P) * sizeof(float);
   static bool configured[64] = {};
-  auto kern = append_rows_kernel<P, BITS, THREADS>;
+  auto kern = append_tile_kernel<P, BITS>;
   if (!configured[g->device & 63]) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM), "append");
     configured[g->device & 63] = true;
   }
   long long items = (long long)a.heads_in_call * a.n_tokens;
-  long long tiles = (items + THREADS - 1) / THREADS;
-  int per_sm = P == 128 ? 3 : 4;
-  int grid = (int)std::min<long long>(tiles, (long long)g->sm_count * per_sm);
-  kern<<<grid, THREADS, SMEM, g->stream>>>(a);
+  long long tiles = (items + AT_TILE - 1) / AT_TILE;
+  int grid = (int)std::min<long long>(tiles, (long long)g->sm_count * 2);
+  kern<<<grid, AT_THREADS, SMEM, g->stream>>>(a);
   ++g_launches;
   CUDA_TRY(cudaGetLastError(), "append");
   return true;
@@ -335,7 +333,8 @@ bool launch_append_one(Group *g, AppendLaunch a, int src_row_align_ok) {
   const CacheView &c = g->c;
   const int bits = a.which ? c.v_bits : c.k_bits;
   const int policy = g_policy.load();
-  bool fast = policy != 1 && (c.padded == 64 || c.padded == 128) && (c.dim % 4 == 0) && src_row_align_ok;
+  const bool small = (long long)a.heads_in_call * a.n_tokens < (1ll << 31) && (long long)a.ring_head + a.n_tokens < (1ll << 31);
+  bool fast = policy != 1 && (c.padded == 64 || c.padded == 128) && (c.dim % 4 == 0) && src_row_align_ok && small;
   if (fast) return c.padded == 128 ? launch_rows_bits<128>(g, a, bits) : launch_rows_bits<64>(g, a, bits);
   if (policy == 2) { set_error("append: shape not covered by the specialised kernel"); return false; }
   long long items = (long long)a.heads_in_call * a.n_tokens;

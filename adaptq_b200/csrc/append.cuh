@@ -59,53 +59,76 @@ __device__ __forceinline__ ItemPlace place_item(const AppendLaunch &a, long long
   return p;
 }
 
+// Same, with 32-bit arithmetic (the tile kernel is only used below 2^31 items).
+__device__ __forceinline__ ItemPlace place_item32(const AppendLaunch &a, uint32_t g) {
+  ItemPlace p;
+  uint32_t hl;
+  if (a.head_major) {
+    hl = g / (uint32_t)a.n_tokens;
+    p.t = (int)(g - hl * (uint32_t)a.n_tokens);
+  } else {
+    p.t = (int)(g / (uint32_t)a.heads_in_call);
+    hl = g - (uint32_t)p.t * (uint32_t)a.heads_in_call;
+  }
+  p.h = a.head0 + (int)hl;
+  const int cap = a.c.cap, T = a.n_tokens;
+  p.store = cap > 0 && p.t >= T - cap;
+  p.slot = cap > 0 ? (int)(((uint32_t)a.ring_head + (uint32_t)p.t) % (uint32_t)cap) : 0;
+  const bool call_evicts = (long long)a.ring_size + T > cap;
+  p.mirror = a.c.hyb > 0 && !call_evicts && (a.mirror_cnt + p.t < a.c.hyb);
+  return p;
+}
+
 __device__ __forceinline__ const float *item_src(const AppendLaunch &a, const ItemPlace &p) {
   return a.src + (size_t)p.t * a.src_token_stride + (size_t)(p.h - a.head0) * a.c.dim;
 }
 
 // ---------------------------------------------------------------------------
-// Register-resident path: one thread owns one vector (P floats in registers).
+// Building blocks of the tile kernel (register-resident path).
 // ---------------------------------------------------------------------------
 
-// Threshold search through a 16-entry shared-memory table over |v| in steps of
-// 0.25 (the last entry takes everything from 3.75 up): every such bucket holds
-// at most one of the positive midpoints of the 2-, 3- and 4-bit codebooks, so
-// an entry is {bits of that midpoint or 0xFFFFFFFF, number of midpoints below
-// the bucket}.  16 entries of 8 bytes span the 32 banks exactly once: lookups
-// never conflict.  With a = |v| as an integer (one less for negative v, which
-// turns the comparison into the strict one the mirrored negative midpoints
-// need),
-//   m = entry.count + (a >= entry.midpoint),  index = m ^ (v < 0 ? half-1 : half)
-// equals upstream's binary search (core/codebook.cpp:119-144) for every
-// non-NaN v.  Used only on vectors where NaN cannot occur.
-constexpr int QT_ENTRIES = 16;
+// Threshold search through a 32-entry shared-memory table: 16 buckets of width
+// 0.25 over |v| (the last takes everything from 3.75 up) for v >= +0 and 16 for
+// the sign bit set.  No bucket holds more than one decision threshold of the
+// 2-, 3- or 4-bit codebooks (the exact 0 in the middle belongs to bucket 0 of
+// both halves), so an entry is {that threshold as a signed float, or +inf;
+// number of thresholds below the bucket}, and
+//   index = entry.count + (v >= entry.threshold)
+// is upstream's binary search with its `v >= t` decisions
+// (core/codebook.cpp:119-144) for every finite v, including -0.0.  32 entries
+// of 8 bytes; the two halves of the table are used by disjoint sets of lanes
+// only by chance, so a lookup can see a 2-way bank conflict at worst.
+constexpr int QT_ENTRIES = 32;
 
 template <int BITS> __device__ __forceinline__ void build_quant_table(uint2 *qtab, int tid) {
-  constexpr int HALF = 1 << (BITS - 1);
+  constexpr int NT = (1 << BITS) - 1; // thresholds, ascending
   if (tid < QT_ENTRIES) {
-    const float lo = 0.25f * (float)tid, hi = tid == QT_ENTRIES - 1 ? INFINITY : 0.25f * (float)(tid + 1);
-    uint32_t m = 0, thr = 0xFFFFFFFFu;
-    for (int k = 0; k < HALF - 1; ++k) {
-      const float pk = c_thr[BITS - 2][HALF + k];
-      if (pk < lo) ++m;
-      else if (pk < hi) thr = __float_as_uint(pk);
+    const int k = tid & 15;
+    const bool negative = tid >= 16;
+    // bucket as an interval of v:  [k/4, (k+1)/4)  or  (-(k+1)/4, -k/4]
+    const float lo = 0.25f * (float)k, hi = k == 15 ? INFINITY : 0.25f * (float)(k + 1);
+    uint32_t below = 0;
+    float thr = INFINITY;
+    for (int j = 0; j < NT; ++j) {
+      const float t = c_thr[BITS - 2][j];
+      const bool inside = negative ? (t > -hi && t <= -lo) : (t >= lo && t < hi);
+      const bool under = negative ? (t <= -hi) : (t < lo);
+      if (under) ++below;
+      if (inside) thr = t;
     }
-    qtab[tid] = make_uint2(thr, m);
+    qtab[tid] = make_uint2(__float_as_uint(thr), below);
   }
 }
 
 template <int BITS> __device__ __forceinline__ uint32_t quantize_lookup(float v, uint32_t qtab_addr) {
-  constexpr uint32_t HALF = 1u << (BITS - 1);
-  const bool neg = v < 0.0f;
-  uint32_t a = __float_as_uint(v) & 0x7FFFFFFFu;
-  a -= neg ? 1u : 0u;
-  // floor(4*min(|v|, 3.99)) lands in the low mantissa bits of 2^23 + 4|v| rounded down
-  const float t = __fmaf_rd(fminf(__uint_as_float(a), 3.99f), 4.0f, 8388608.0f);
-  const uint32_t addr = (__float_as_uint(t) << 3) + (qtab_addr - 0x58000000u); // (bits - 0x4B000000) * 8
+  // floor(4*min(|v|, 3.99)) lands in the low mantissa bits of 2^23 + 4|v| rounded down;
+  // the sign bit selects the upper half of the table
+  const float t = __fmaf_rd(fminf(fabsf(v), 3.99f), 4.0f, 8388608.0f);
+  const uint32_t key = ((__float_as_uint(v) >> 27) & 16u) | __float_as_uint(t); // 0x4B000000 + bucket
+  const uint32_t addr = (key << 3) + (qtab_addr - 0x58000000u);                 // (key - 0x4B000000) * 8
   uint2 e;
   asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "r"(addr));
-  const uint32_t m = e.y + (a >= e.x ? 1u : 0u);
-  return m ^ (neg ? HALF - 1u : HALF);
+  return e.y + (v >= __uint_as_float(e.x) ? 1u : 0u);
 }
 
 // Bit position of coordinate k of a packed 32-bit word (MSB-first within bytes).
@@ -137,95 +160,6 @@ __device__ __forceinline__ void mul2(float &a, float &b, unsigned long long m) {
   const unsigned long long v = pack2(a, b);
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(v), "l"(m));
   unpack2(r, a, b);
-}
-
-// Returns false (and leaves `w` untouched) for the rare vectors that need the
-// literal clip path; the caller re-does those with the general routine.
-template <int P, int BITS>
-__device__ __forceinline__ bool quantize_row_regs(float (&x)[P], const uint32_t (&sg)[(P + 31) / 32],
-                                                  uint32_t (&w)[(P * BITS + 31) / 32], uint32_t qtab_addr,
-                                                  float &norm_out) {
-  // L2 norm: a strictly sequential chain, multiply and add rounded separately
-  // (core/quantizer.cpp:59-66).  The squares are independent and go two at a time.
-  float norm = 0.f;
-#pragma unroll
-  for (int i = 0; i < P; i += 2) {
-    float s0 = x[i], s1 = x[i + 1];
-    mul2(s0, s1, pack2(x[i], x[i + 1]));
-    norm = __fadd_rn(norm, s0);
-    norm = __fadd_rn(norm, s1);
-  }
-  const bool all_zero = norm == 0.f;
-  norm = __fsqrt_rn(__fadd_rn(norm, 1e-12f));
-  norm_out = norm;
-  // The +-3 sigma clip (core/quantizer.cpp:81-89) can only change an index when
-  // 3*sigma falls below the largest midpoint (2.1476).  sigma^2 equals
-  // (norm^2 - 1e-12)/norm^2 up to rounding, so for norm >= 1e-5 it is >= 0.98 and
-  // the clip is a no-op; a finite norm also rules out NaN.  An all-zero vector
-  // quantises to the middle index with or without the clip.  Everything else
-  // (tiny, infinite or NaN norms) is left to the general routine.
-  if (!((norm >= 1e-5f && norm < INFINITY) || all_zero)) return false;
-
-  const float inv = __fdiv_rn(1.0f, norm);
-  const unsigned long long inv2 = pack2(inv, inv);
-  // normalise, then the Rademacher sign (a sign-bit XOR equals the multiply by +-1)
-#pragma unroll
-  for (int i = 0; i < P; i += 2) {
-    mul2(x[i], x[i + 1], inv2);
-    x[i] = __uint_as_float(__float_as_uint(x[i]) ^ ((sg[i >> 5] << (31 - (i & 31))) & 0x80000000u));
-    x[i + 1] = __uint_as_float(__float_as_uint(x[i + 1]) ^ ((sg[i >> 5] << (30 - (i & 31))) & 0x80000000u));
-  }
-  // butterflies in upstream's stage order (core/fwht.cpp:36-57): len = 1 pairs
-  // neighbours, every later stage moves two neighbouring butterflies at once
-#pragma unroll
-  for (int i = 0; i < P; i += 2) {
-    const float a = x[i], b = x[i + 1];
-    x[i] = __fadd_rn(a, b);
-    x[i + 1] = __fsub_rn(a, b);
-  }
-#pragma unroll
-  for (int len = 2; len < P; len <<= 1) {
-#pragma unroll
-    for (int i = 0; i < P; i += (len << 1)) {
-#pragma unroll
-      for (int j = 0; j < len; j += 2) butterfly2(x[i + j], x[i + j + 1], x[i + j + len], x[i + j + len + 1]);
-    }
-  }
-  // x * (1/sqrt p) [core/fwht.cpp:60-65]  then * sqrt p [core/quantizer.cpp:73-75]
-  const float sq = __fsqrt_rn((float)P);
-  const float isq = __fdiv_rn(1.0f, sq);
-  const unsigned long long sq2 = pack2(sq, sq), isq2 = pack2(isq, isq);
-#pragma unroll
-  for (int i = 0; i < P; i += 2) {
-    mul2(x[i], x[i + 1], isq2);
-    mul2(x[i], x[i + 1], sq2);
-  }
-  if (BITS == 3) { // 8 indices -> 3 bytes, big-endian bit order
-#pragma unroll
-    for (int i = 0; i < P; i += 32) {
-      uint32_t r[4];
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint32_t v24 = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) v24 |= quantize_lookup<3>(x[i + g * 8 + k], qtab_addr) << (21 - 3 * k);
-        r[g] = __byte_perm(v24, 0, 0x3012); // memory image of the three bytes, first byte lowest
-      }
-      w[(i >> 5) * 3 + 0] = r[0] | (r[1] << 24);
-      w[(i >> 5) * 3 + 1] = (r[1] >> 8) | (r[2] << 16);
-      w[(i >> 5) * 3 + 2] = (r[2] >> 16) | (r[3] << 8);
-    }
-  } else {
-    constexpr int PER = 32 / BITS;
-#pragma unroll
-    for (int i = 0; i < P; i += PER) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int k = 0; k < PER; ++k) word |= quantize_lookup<BITS>(x[i + k], qtab_addr) << index_shift<BITS>(k);
-      w[i / PER] = word;
-    }
-  }
-  return true;
 }
 
 // ---------------------------------------------------------------------------
@@ -322,49 +256,170 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) append_general_kernel(const Ap
 }
 
 // ---------------------------------------------------------------------------
-// One block = THREADS vectors per tile; rows arrive in shared memory through
-// per-row bulk (TMA) copies, each thread then pulls its row into registers,
-// and the next tile's copies are issued before the arithmetic starts.  The
-// few vectors the register path declines are listed and redone by the general
-// routine before the block moves on.
+// Tile kernel.  One block = 512 threads works on tiles of 128 vectors whose
+// rows arrive in shared memory through per-row bulk (TMA) copies.
+//
+//  pass 1  one thread per vector walks its row and forms the L2 norm as the
+//          strictly sequential chain upstream computes (the only part that
+//          cannot be split across lanes without changing the rounding);
+//  pass 2  four lanes share a vector, each holding a contiguous quarter
+//          (32 floats at dim 128) in registers: normalise, sign, butterflies
+//          -- the first stages inside a lane, the last two across lanes with
+//          shuffles, in upstream's stage order --, scaling, table quantiser,
+//          bit packing; every lane stores the contiguous 16/12/8 bytes of the
+//          packed row that its quarter produces.
+//
+// 64 data registers per vector quarter instead of 128 per vector is what
+// lets 32 warps live on an SM (the arithmetic is a long dependent sequence,
+// so it is occupancy that hides its latency).  The next tile's copies are
+// issued as soon as every lane has pulled its quarter into registers.  The
+// few vectors the table quantiser may not handle (tiny, infinite or NaN
+// norms) are listed in pass 1 and redone by the general routine.
 // ---------------------------------------------------------------------------
-template <int P, int BITS, int THREADS>
-__global__ void __launch_bounds__(THREADS, (P == 128 ? 3 : 4))
-append_rows_kernel(const AppendLaunch a) {
-  constexpr int PITCH = P + 4; // floats; +16 B keeps 128-bit row reads conflict-free
+constexpr int AT_TILE = 128;
+constexpr int AT_THREADS = 512;
+
+template <int NBYTES> __device__ __forceinline__ void store_packed(uint8_t *dst, const uint32_t *w) {
+  if constexpr (NBYTES == 16) {
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else if constexpr (NBYTES == 12) {
+    uint32_t *d = reinterpret_cast<uint32_t *>(dst);
+    d[0] = w[0]; d[1] = w[1]; d[2] = w[2];
+  } else if constexpr (NBYTES == 8) {
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(w[0], w[1]);
+  } else if constexpr (NBYTES == 6) {
+    uint16_t *d = reinterpret_cast<uint16_t *>(dst);
+    d[0] = (uint16_t)w[0]; d[1] = (uint16_t)(w[0] >> 16); d[2] = (uint16_t)w[1];
+  } else {
+    static_assert(NBYTES == 4, "unexpected packed slice size");
+    *reinterpret_cast<uint32_t *>(dst) = w[0];
+  }
+}
+
+// Quarter-vector transform + quantisation.  x: this lane's EPL = P/4 contiguous
+// coordinates (already loaded), `part` = which quarter, sgw = the sign bits of
+// those coordinates in bits 0..EPL-1.  Produces EPL*BITS/8 packed bytes in w.
+template <int P, int BITS>
+__device__ __forceinline__ void quantize_quarter(float (&x)[P / 4], float norm, uint32_t sgw, int lane,
+                                                 uint32_t (&w)[(P / 4 * BITS + 31) / 32], uint32_t qtab_addr) {
+  constexpr int EPL = P / 4;
+  const float inv = __fdiv_rn(1.0f, norm);
+  const unsigned long long inv2 = pack2(inv, inv);
+#pragma unroll
+  for (int i = 0; i < EPL; i += 2) {
+    mul2(x[i], x[i + 1], inv2);
+    x[i] = __uint_as_float(__float_as_uint(x[i]) ^ ((sgw << (31 - i)) & 0x80000000u));
+    x[i + 1] = __uint_as_float(__float_as_uint(x[i + 1]) ^ ((sgw << (30 - i)) & 0x80000000u));
+  }
+  // stages len = 1 .. EPL/2 stay inside the lane (core/fwht.cpp:36-57)
+#pragma unroll
+  for (int i = 0; i < EPL; i += 2) {
+    const float a = x[i], b = x[i + 1];
+    x[i] = __fadd_rn(a, b);
+    x[i + 1] = __fsub_rn(a, b);
+  }
+#pragma unroll
+  for (int len = 2; len < EPL; len <<= 1) {
+#pragma unroll
+    for (int i = 0; i < EPL; i += (len << 1)) {
+#pragma unroll
+      for (int j = 0; j < len; j += 2) butterfly2(x[i + j], x[i + j + 1], x[i + j + len], x[i + j + len + 1]);
+    }
+  }
+  // stages len = EPL and 2*EPL pair this lane with the lanes 8 and 16 away: the
+  // lower quarter keeps a+b, the upper one a-b.  Both are partner + (+-1)*mine in
+  // one fused multiply-add, which rounds exactly like the plain add or subtract.
+#pragma unroll
+  for (int m = 8; m <= 16; m <<= 1) {
+    const float sgn = (lane & m) ? -1.0f : 1.0f;
+    const unsigned long long sgn2 = pack2(sgn, sgn);
+#pragma unroll
+    for (int i = 0; i < EPL; i += 2) {
+      const float o0 = __shfl_xor_sync(0xffffffffu, x[i], m), o1 = __shfl_xor_sync(0xffffffffu, x[i + 1], m);
+      unsigned long long r;
+      asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(pack2(x[i], x[i + 1])), "l"(sgn2), "l"(pack2(o0, o1)));
+      unpack2(r, x[i], x[i + 1]);
+    }
+  }
+  // x * (1/sqrt p) [core/fwht.cpp:60-65]  then * sqrt p [core/quantizer.cpp:73-75]
+  const float sq = __fsqrt_rn((float)P);
+  const float isq = __fdiv_rn(1.0f, sq);
+  const unsigned long long sq2 = pack2(sq, sq), isq2 = pack2(isq, isq);
+#pragma unroll
+  for (int i = 0; i < EPL; i += 2) {
+    mul2(x[i], x[i + 1], isq2);
+    mul2(x[i], x[i + 1], sq2);
+  }
+  if constexpr (BITS == 3) { // 8 indices -> 3 bytes, big-endian bit order
+    uint32_t r[EPL / 8];
+#pragma unroll
+    for (int g = 0; g < EPL / 8; ++g) {
+      uint32_t v24 = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v24 += quantize_lookup<3>(x[g * 8 + k], qtab_addr) << (21 - 3 * k);
+      r[g] = __byte_perm(v24, 0, 0x3012); // memory image of the three bytes, first byte lowest
+    }
+    if constexpr (EPL == 32) {
+      w[0] = r[0] | (r[1] << 24);
+      w[1] = (r[1] >> 8) | (r[2] << 16);
+      w[2] = (r[2] >> 16) | (r[3] << 8);
+    } else {
+      w[0] = r[0] | (r[1] << 24);
+      w[1] = r[1] >> 8;
+    }
+  } else {
+    constexpr int PER = 32 / BITS;
+#pragma unroll
+    for (int i = 0; i < EPL; i += PER) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < PER; ++k) word += quantize_lookup<BITS>(x[i + k], qtab_addr) << index_shift<BITS>(k);
+      w[i / PER] = word;
+    }
+  }
+}
+
+template <int P, int BITS>
+__global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const AppendLaunch a) {
+  constexpr int EPL = P / 4;     // coordinates per lane
+  constexpr int PITCH = P + 4;   // floats; +16 B keeps both passes' 128-bit reads conflict-free
+  constexpr int QB = BITS == 16 ? 4 : BITS;
   extern __shared__ __align__(128) unsigned char smem_rows[];
   float *tile = reinterpret_cast<float *>(smem_rows);
-  float *redo_buf = tile + (size_t)THREADS * PITCH; // (THREADS/32) x P floats
+  float *redo_buf = tile + (size_t)AT_TILE * PITCH; // (AT_THREADS/32) x P floats for the general routine
   __shared__ __align__(8) uint64_t bar;
   __shared__ __align__(16) uint2 qtab[QT_ENTRIES];
+  __shared__ float s_norm[AT_TILE];
   __shared__ int redo_count;
-  __shared__ int redo_list[THREADS];
+  __shared__ int redo_list[AT_TILE];
 
-  const int tid = threadIdx.x;
-  if constexpr (BITS != 16) build_quant_table<BITS>(qtab, tid);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int vt = warp * 8 + (lane & 7); // vector of the tile this lane works on in pass 2
+  const int part = lane >> 3;           // which quarter of it
+  if constexpr (BITS != 16) build_quant_table<QB>(qtab, tid);
   const uint32_t qtab_addr = smem_u32(qtab);
+  const CacheView &c = a.c;
   const long long n_items = (long long)a.heads_in_call * a.n_tokens;
-  const long long n_tiles = (n_items + THREADS - 1) / THREADS;
-  const int dim = a.c.dim;
+  const long long n_tiles = (n_items + AT_TILE - 1) / AT_TILE;
+  const int dim = c.dim;
   const uint32_t row_bytes_in = (uint32_t)dim * 4u;
-  float *my_row = tile + (size_t)tid * PITCH;
 
   if (tid == 0) {
-    mbar_init(&bar, THREADS);
+    mbar_init(&bar, AT_TILE);
     fence_barrier_init();
     redo_count = 0;
   }
-  // zero the padding columns once (dim < P); bulk copies never touch them
-  for (int i = dim; i < P; ++i) my_row[i] = 0.f;
+  if (tid < AT_TILE) // zero the padding columns once (dim < P); bulk copies never touch them
+    for (int i = dim; i < P; ++i) tile[(size_t)tid * PITCH + i] = 0.f;
   __syncthreads();
 
-  auto issue = [&](long long tile_idx) {
-    long long g = tile_idx * THREADS + tid;
+  auto issue = [&](long long tile_idx) { // threads 0..127: one row each
+    const long long g = tile_idx * AT_TILE + tid;
     if (g < n_items) {
-      ItemPlace p = place_item(a, g);
+      const ItemPlace p = place_item32(a, (uint32_t)g);
       if (p.store || p.mirror) {
         mbar_expect_tx(&bar, row_bytes_in);
-        bulk_g2s(my_row, item_src(a, p), row_bytes_in, &bar);
+        bulk_g2s(tile + (size_t)tid * PITCH, item_src(a, p), row_bytes_in, &bar);
         return;
       }
     }
@@ -372,7 +427,7 @@ append_rows_kernel(const AppendLaunch a) {
   };
 
   long long tile_idx = blockIdx.x;
-  if (tile_idx < n_tiles) issue(tile_idx);
+  if (tile_idx < n_tiles && tid < AT_TILE) issue(tile_idx);
   uint32_t parity = 0;
   for (; tile_idx < n_tiles; tile_idx += gridDim.x) {
     if (!mbar_wait(&bar, parity)) {
@@ -380,73 +435,99 @@ append_rows_kernel(const AppendLaunch a) {
       return;
     }
     parity ^= 1u;
-    const long long g = tile_idx * THREADS + tid;
+
+    // ---- pass 1: sequential norms (core/quantizer.cpp:59-66), one thread per vector ----
+    if (BITS != 16 && tid < AT_TILE) {
+      const long long g = tile_idx * AT_TILE + tid;
+      bool live = false;
+      if (g < n_items) live = place_item32(a, (uint32_t)g).store;
+      if (live) {
+        const float4 *r4 = reinterpret_cast<const float4 *>(tile + (size_t)tid * PITCH);
+        float sum = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < P / 4; ++i) {
+          const float4 v = r4[i];
+          float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
+          mul2(s0, s1, pack2(v.x, v.y));
+          mul2(s2, s3, pack2(v.z, v.w));
+          sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, s0), s1), s2), s3);
+        }
+        const bool all_zero = sum == 0.f;
+        const float norm = __fsqrt_rn(__fadd_rn(sum, 1e-12f));
+        // norm >= 1e-5 makes the +-3 sigma clip a no-op and rules out NaN (see
+        // quantize_lookup); an all-zero vector quantises to the middle index either way
+        const bool plain = (norm >= 1e-5f && norm < INFINITY) || all_zero;
+        s_norm[tid] = plain ? norm : -1.f;
+        if (!plain) redo_list[atomicAdd(&redo_count, 1)] = tid;
+      } else {
+        s_norm[tid] = -1.f;
+      }
+    }
+
+    // ---- pass 2: four lanes per vector -------------------------------------------------
+    const long long g = tile_idx * AT_TILE + vt;
     ItemPlace p;
     p.store = p.mirror = false;
-    if (g < n_items) p = place_item(a, g);
-    float x[P];
-    if (p.store || p.mirror) {
-      const float4 *r4 = reinterpret_cast<const float4 *>(my_row);
+    if (g < n_items) p = place_item32(a, (uint32_t)g);
+    float x[EPL];
+    {
+      const bool have = p.store || p.mirror;
+      const float4 *r4 = reinterpret_cast<const float4 *>(tile + (size_t)vt * PITCH + part * EPL);
 #pragma unroll
-      for (int i = 0; i < P / 4; ++i) {
-        float4 v = r4[i];
+      for (int i = 0; i < EPL / 4; ++i) {
+        const float4 v = have ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
       }
     }
-    __syncthreads(); // every row has been read; the tile buffer is free
+    __syncthreads(); // rows are in registers, norms are published; the tile buffer is free
+    const float norm = BITS == 16 ? 1.f : s_norm[vt];
     const long long next = tile_idx + gridDim.x;
-    if (next < n_tiles) {
+    if (next < n_tiles && tid < AT_TILE) {
       fence_proxy_async();
       issue(next);
     }
     if (p.mirror) {
-      float4 *m4 = reinterpret_cast<float4 *>(a.c.mirror + (size_t)p.h * a.c.mirror_stride +
-                                              (size_t)p.slot * 2 * dim + (a.which ? dim : 0));
+      float4 *m4 = reinterpret_cast<float4 *>(c.mirror + (size_t)p.h * c.mirror_stride + (size_t)p.slot * 2 * dim +
+                                              (a.which ? dim : 0) + part * EPL);
 #pragma unroll
-      for (int i = 0; i < P / 4; ++i)
-        if (4 * i < dim) m4[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+      for (int i = 0; i < EPL / 4; ++i)
+        if (part * EPL + 4 * i < dim) m4[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
     }
-    if (p.store) {
-      const CacheView &c = a.c;
-      uint8_t *slab = a.which ? c.v_slab : c.k_slab;
-      const size_t stride = a.which ? c.v_stride : c.k_stride;
-      float *scale = (a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride + p.slot;
-      if constexpr (BITS == 16) {
-        float4 *dst = reinterpret_cast<float4 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4));
+    if constexpr (BITS == 16) {
+      if (p.store) {
+        uint8_t *slab = a.which ? c.v_slab : c.k_slab;
+        const size_t stride = a.which ? c.v_stride : c.k_stride;
+        float4 *dst = reinterpret_cast<float4 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4)) + part * (EPL / 4);
 #pragma unroll
-        for (int i = 0; i < P / 4; ++i) dst[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
-        *scale = 1.0f;
-      } else {
-        constexpr int NW = (P * BITS + 31) / 32;
-        uint32_t sg[(P + 31) / 32];
-#pragma unroll
-        for (int i = 0; i < (P + 31) / 32; ++i) sg[i] = c.signs[(size_t)p.h * c.sign_words + i];
-        uint32_t w[NW];
-        float norm;
-        if (quantize_row_regs<P, BITS>(x, sg, w, qtab_addr, norm)) {
-          uint8_t *row = slab + (size_t)p.h * stride + (size_t)p.slot * (NW * 4);
-          if ((NW * 4) % 16 == 0) {
-            uint4 *d4 = reinterpret_cast<uint4 *>(row);
-#pragma unroll
-            for (int i = 0; i < NW / 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-          } else {
-            uint2 *d2 = reinterpret_cast<uint2 *>(row);
-#pragma unroll
-            for (int i = 0; i < NW / 2; ++i) d2[i] = make_uint2(w[2 * i], w[2 * i + 1]);
-          }
-          *scale = norm;
-        } else {
-          redo_list[atomicAdd(&redo_count, 1)] = tid;
-        }
+        for (int i = 0; i < EPL / 4; ++i) dst[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+        if (part == 0) ((a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = 1.0f;
+      }
+    } else {
+      // Every lane runs the transform (its shuffles need the whole warp); lanes whose
+      // vector is not stored here -- ragged tile end, or a vector left to the general
+      // routine -- work on zeros and skip the store.
+      constexpr int NBYTES = EPL * BITS / 8;
+      const bool keep = p.store && norm >= 0.f;
+      uint32_t sgw = 0; // sign bits of this quarter in bits 0..EPL-1
+      if (keep) {
+        sgw = c.signs[(size_t)p.h * c.sign_words + ((part * EPL) >> 5)];
+        if constexpr (EPL < 32) sgw >>= (part * EPL) & 31;
+      }
+      uint32_t w[(EPL * BITS + 31) / 32];
+      quantize_quarter<P, BITS>(x, keep ? norm : 1.f, sgw, lane, w, qtab_addr);
+      if (keep) {
+        uint8_t *slab = a.which ? c.v_slab : c.k_slab;
+        const size_t stride = a.which ? c.v_stride : c.k_stride;
+        store_packed<NBYTES>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * BITS / 8) + part * NBYTES, w);
+        if (part == 0) ((a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = norm;
       }
     }
     if constexpr (BITS != 16) {
       __syncthreads();
       const int n_redo = redo_count;
       if (n_redo > 0) { // rare: tiny, infinite or NaN norms
-        const int warp = tid >> 5, lane = tid & 31;
-        for (int e = warp; e < n_redo; e += THREADS / 32)
-          append_item_general(a, tile_idx * THREADS + redo_list[e], redo_buf + (size_t)warp * P, lane);
+        for (int e = warp; e < n_redo; e += AT_THREADS / 32)
+          append_item_general(a, tile_idx * AT_TILE + redo_list[e], redo_buf + (size_t)warp * P, lane);
         __syncthreads();
         if (tid == 0) redo_count = 0;
       }

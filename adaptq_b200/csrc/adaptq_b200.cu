@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -312,7 +313,7 @@ bool launch_rows(Group *g, const AppendLaunch &a) {
   }
   long long items = (long long)a.heads_in_call * a.n_tokens;
   long long tiles = (items + AT_TILE - 1) / AT_TILE;
-  int grid = (int)std::min<long long>(tiles, (long long)g->sm_count * 2);
+  int grid = (int)std::min<long long>(tiles, (long long)g->sm_count * AT_BLOCKS_PER_SM);
   kern<<<grid, AT_THREADS, SMEM, g->stream>>>(a);
   ++g_launches;
   CUDA_TRY(cudaGetLastError(), "append");
@@ -346,6 +347,18 @@ bool launch_append_one(Group *g, AppendLaunch a, int src_row_align_ok) {
   return true;
 }
 
+// (magic, shift, add) with  x / d == umulhi(x + add, magic) >> shift  for 0 <= x < 2^31
+// (round-down multiplier; the +1 on the dividend makes it exact).
+void magic_div(uint32_t d, uint32_t &magic, uint32_t &shift, uint32_t &add) {
+  if (d <= 1) { magic = 0xFFFFFFFFu; shift = 0; add = 1; return; }
+  uint32_t l = 0;
+  while ((1ull << l) < d) ++l; // ceil(log2 d)
+  if ((d & (d - 1)) == 0) { magic = 0x80000000u; shift = l - 1; add = 0; return; }
+  magic = (uint32_t)((1ull << (32 + l - 1)) / d);
+  shift = l - 1;
+  add = 1;
+}
+
 RingState advance(const CacheView &c, RingState s, int T) { // cache/ring_buffer.cpp:105-119, attention.cpp:354-365
   RingState r = s;
   if (c.cap > 0) {
@@ -371,6 +384,13 @@ bool append_device(Group *g, const float *dk, const float *dv, int head0, int he
   a.head_major = n_tokens >= 32;
   a.status = g->d_status;
   a.src_token_stride = token_stride;
+  magic_div((uint32_t)(a.head_major ? n_tokens : heads_in_call), a.div_magic, a.div_shift, a.div_add);
+  magic_div((uint32_t)std::max(1, g->c.cap), a.cap_magic, a.cap_shift, a.cap_add);
+  {
+    volatile float sq = sqrtf((float)g->c.padded); // IEEE sqrt, then IEEE divide, as upstream computes them
+    volatile float isq = 1.0f / sq;
+    a.sqrt_p = sq; a.inv_sqrt_p = isq;
+  }
   for (int which = 0; which < 2; ++which) {
     a.which = which;
     a.src = which ? dv : dk;

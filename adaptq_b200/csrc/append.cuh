@@ -26,6 +26,12 @@ struct AppendLaunch {
   int ring_head, ring_size, mirror_cnt; // state shared by the heads of this call
   int head_major;
   int *status;
+  // exact division of 32-bit values by the item divisor (n_tokens when head_major,
+  // else heads_in_call) and by the ring capacity: q = umulhi(x, magic) >> shift
+  // after adding `add` (round-up variant), filled in by the host
+  uint32_t div_magic, div_shift, div_add;
+  uint32_t cap_magic, cap_shift, cap_add;
+  float sqrt_p, inv_sqrt_p; // sqrtf(padded) and 1/sqrtf(padded), IEEE-rounded on the host
 };
 
 struct ItemPlace {
@@ -59,21 +65,29 @@ __device__ __forceinline__ ItemPlace place_item(const AppendLaunch &a, long long
   return p;
 }
 
-// Same, with 32-bit arithmetic (the tile kernel is only used below 2^31 items).
+// x / d for x < 2^31 with the host-computed (magic, shift, add) of d.
+__device__ __forceinline__ uint32_t fast_div(uint32_t x, uint32_t magic, uint32_t shift, uint32_t add) {
+  return __umulhi(x + add, magic) >> shift;
+}
+
+// Same as place_item with 32-bit arithmetic and multiply-shift divisions (the
+// tile kernel is only used below 2^31 items).
 __device__ __forceinline__ ItemPlace place_item32(const AppendLaunch &a, uint32_t g) {
   ItemPlace p;
   uint32_t hl;
+  const uint32_t q = fast_div(g, a.div_magic, a.div_shift, a.div_add);
   if (a.head_major) {
-    hl = g / (uint32_t)a.n_tokens;
-    p.t = (int)(g - hl * (uint32_t)a.n_tokens);
+    hl = q;
+    p.t = (int)(g - q * (uint32_t)a.n_tokens);
   } else {
-    p.t = (int)(g / (uint32_t)a.heads_in_call);
-    hl = g - (uint32_t)p.t * (uint32_t)a.heads_in_call;
+    p.t = (int)q;
+    hl = g - q * (uint32_t)a.heads_in_call;
   }
   p.h = a.head0 + (int)hl;
   const int cap = a.c.cap, T = a.n_tokens;
   p.store = cap > 0 && p.t >= T - cap;
-  p.slot = cap > 0 ? (int)(((uint32_t)a.ring_head + (uint32_t)p.t) % (uint32_t)cap) : 0;
+  const uint32_t pos = (uint32_t)a.ring_head + (uint32_t)p.t;
+  p.slot = cap > 0 ? (int)(pos - fast_div(pos, a.cap_magic, a.cap_shift, a.cap_add) * (uint32_t)cap) : 0;
   const bool call_evicts = (long long)a.ring_size + T > cap;
   p.mirror = a.c.hyb > 0 && !call_evicts && (a.mirror_cnt + p.t < a.c.hyb);
   return p;
@@ -87,45 +101,37 @@ __device__ __forceinline__ const float *item_src(const AppendLaunch &a, const It
 // Building blocks of the tile kernel (register-resident path).
 // ---------------------------------------------------------------------------
 
-// Threshold search through a 32-entry shared-memory table: 16 buckets of width
-// 0.25 over |v| (the last takes everything from 3.75 up) for v >= +0 and 16 for
-// the sign bit set.  No bucket holds more than one decision threshold of the
-// 2-, 3- or 4-bit codebooks (the exact 0 in the middle belongs to bucket 0 of
-// both halves), so an entry is {that threshold as a signed float, or +inf;
-// number of thresholds below the bucket}, and
+// Threshold search through a shared-memory table indexed by floor(4v) + 64: the
+// 128 buckets [k/4, (k+1)/4), k = -64..63, cover |v| < 16 (transformed
+// coordinates of a unit vector never exceed sqrt(p) <= 11.4 in magnitude).  No
+// bucket holds more than one decision threshold of the 2-, 3- or 4-bit
+// codebooks, so an entry is {that threshold, or +inf; number of thresholds
+// below the bucket}, and
 //   index = entry.count + (v >= entry.threshold)
 // is upstream's binary search with its `v >= t` decisions
-// (core/codebook.cpp:119-144) for every finite v, including -0.0.  32 entries
-// of 8 bytes; the two halves of the table are used by disjoint sets of lanes
-// only by chance, so a lookup can see a 2-way bank conflict at worst.
-constexpr int QT_ENTRIES = 32;
+// (core/codebook.cpp:119-144) for every finite v in range, including -0.0
+// (4*(-0.0) + C rounds to C, i.e. to the bucket that holds the exact 0).
+constexpr int QT_ENTRIES = 128;
 
-template <int BITS> __device__ __forceinline__ void build_quant_table(uint2 *qtab, int tid) {
+template <int BITS> __device__ __forceinline__ void build_quant_table(uint2 *qtab, int tid, int nthreads) {
   constexpr int NT = (1 << BITS) - 1; // thresholds, ascending
-  if (tid < QT_ENTRIES) {
-    const int k = tid & 15;
-    const bool negative = tid >= 16;
-    // bucket as an interval of v:  [k/4, (k+1)/4)  or  (-(k+1)/4, -k/4]
-    const float lo = 0.25f * (float)k, hi = k == 15 ? INFINITY : 0.25f * (float)(k + 1);
+  for (int e = tid; e < QT_ENTRIES; e += nthreads) {
+    const float lo = 0.25f * (float)(e - 64), hi = 0.25f * (float)(e - 63);
     uint32_t below = 0;
     float thr = INFINITY;
     for (int j = 0; j < NT; ++j) {
       const float t = c_thr[BITS - 2][j];
-      const bool inside = negative ? (t > -hi && t <= -lo) : (t >= lo && t < hi);
-      const bool under = negative ? (t <= -hi) : (t < lo);
-      if (under) ++below;
-      if (inside) thr = t;
+      if (t < lo) ++below;
+      else if (t < hi) thr = t;
     }
-    qtab[tid] = make_uint2(__float_as_uint(thr), below);
+    qtab[e] = make_uint2(__float_as_uint(thr), below);
   }
 }
 
 template <int BITS> __device__ __forceinline__ uint32_t quantize_lookup(float v, uint32_t qtab_addr) {
-  // floor(4*min(|v|, 3.99)) lands in the low mantissa bits of 2^23 + 4|v| rounded down;
-  // the sign bit selects the upper half of the table
-  const float t = __fmaf_rd(fminf(fabsf(v), 3.99f), 4.0f, 8388608.0f);
-  const uint32_t key = ((__float_as_uint(v) >> 27) & 16u) | __float_as_uint(t); // 0x4B000000 + bucket
-  const uint32_t addr = (key << 3) + (qtab_addr - 0x58000000u);                 // (key - 0x4B000000) * 8
+  // floor(4v) + 64 lands in the low mantissa bits of 2^23 + 64 + 4v rounded down
+  const float t = __fmaf_rd(v, 4.0f, 8388608.0f + 64.0f);
+  const uint32_t addr = (__float_as_uint(t) << 3) + (qtab_addr - 0x58000000u); // (bits - 0x4B000000) * 8
   uint2 e;
   asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "r"(addr));
   return e.y + (v >= __uint_as_float(e.x) ? 1u : 0u);
@@ -146,20 +152,6 @@ __device__ __forceinline__ unsigned long long pack2(float a, float b) {
 }
 __device__ __forceinline__ void unpack2(unsigned long long v, float &a, float &b) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ void butterfly2(float &l0, float &l1, float &h0, float &h1) {
-  const unsigned long long L = pack2(l0, l1), H = pack2(h0, h1);
-  unsigned long long S, D;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(S) : "l"(L), "l"(H));
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(D) : "l"(L), "l"(H));
-  unpack2(S, l0, l1);
-  unpack2(D, h0, h1);
-}
-__device__ __forceinline__ void mul2(float &a, float &b, unsigned long long m) {
-  unsigned long long r;
-  const unsigned long long v = pack2(a, b);
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(v), "l"(m));
-  unpack2(r, a, b);
 }
 
 // ---------------------------------------------------------------------------
@@ -276,8 +268,12 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) append_general_kernel(const Ap
 // few vectors the table quantiser may not handle (tiny, infinite or NaN
 // norms) are listed in pass 1 and redone by the general routine.
 // ---------------------------------------------------------------------------
-constexpr int AT_TILE = 128;
-constexpr int AT_THREADS = 512;
+#ifndef AQ_AT_TILE
+#define AQ_AT_TILE 64
+#endif
+constexpr int AT_TILE = AQ_AT_TILE;          // vectors per tile
+constexpr int AT_THREADS = 4 * AT_TILE;      // four lanes per vector
+constexpr int AT_BLOCKS_PER_SM = 1024 / AT_THREADS;
 
 template <int NBYTES> __device__ __forceinline__ void store_packed(uint8_t *dst, const uint32_t *w) {
   if constexpr (NBYTES == 16) {
@@ -296,34 +292,59 @@ template <int NBYTES> __device__ __forceinline__ void store_packed(uint8_t *dst,
   }
 }
 
-// Quarter-vector transform + quantisation.  x: this lane's EPL = P/4 contiguous
-// coordinates (already loaded), `part` = which quarter, sgw = the sign bits of
-// those coordinates in bits 0..EPL-1.  Produces EPL*BITS/8 packed bytes in w.
+// Packed-pair helpers: a 64-bit register pair holds coordinates (2i, 2i+1).
+__device__ __forceinline__ unsigned long long mulp(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long addp(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long subp(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long fmap(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// Quarter-vector transform + quantisation.  xp: this lane's EPL = P/4 contiguous
+// coordinates as EPL/2 packed pairs (they stay packed throughout, so the f32x2
+// instructions need no register shuffling), sgw = the sign bits of those
+// coordinates in bits 0..EPL-1.  Produces EPL*BITS/8 packed bytes in w.
 template <int P, int BITS>
-__device__ __forceinline__ void quantize_quarter(float (&x)[P / 4], float norm, uint32_t sgw, int lane,
-                                                 uint32_t (&w)[(P / 4 * BITS + 31) / 32], uint32_t qtab_addr) {
-  constexpr int EPL = P / 4;
-  const float inv = __fdiv_rn(1.0f, norm);
+__device__ __forceinline__ void quantize_quarter(unsigned long long (&xp)[P / 8], float inv, float sq, float isq,
+                                                 uint32_t sgw, int lane, uint32_t (&w)[(P / 4 * BITS + 31) / 32],
+                                                 uint32_t qtab_addr) {
+  constexpr int EPL = P / 4, NP = EPL / 2;
   const unsigned long long inv2 = pack2(inv, inv);
+  // normalise, Rademacher sign (a sign-bit XOR equals the multiply by +-1), and the
+  // len = 1 stage, which pairs the two halves of a register pair (core/fwht.cpp:36-42)
 #pragma unroll
-  for (int i = 0; i < EPL; i += 2) {
-    mul2(x[i], x[i + 1], inv2);
-    x[i] = __uint_as_float(__float_as_uint(x[i]) ^ ((sgw << (31 - i)) & 0x80000000u));
-    x[i + 1] = __uint_as_float(__float_as_uint(x[i + 1]) ^ ((sgw << (30 - i)) & 0x80000000u));
+  for (int i = 0; i < NP; ++i) {
+    float a, b;
+    unpack2(mulp(xp[i], inv2), a, b);
+    a = __uint_as_float(__float_as_uint(a) ^ ((sgw << (31 - 2 * i)) & 0x80000000u));
+    b = __uint_as_float(__float_as_uint(b) ^ ((sgw << (30 - 2 * i)) & 0x80000000u));
+    xp[i] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));
   }
-  // stages len = 1 .. EPL/2 stay inside the lane (core/fwht.cpp:36-57)
+  // stages len = 2 .. EPL/2 stay inside the lane: pairs at distance len/2
 #pragma unroll
-  for (int i = 0; i < EPL; i += 2) {
-    const float a = x[i], b = x[i + 1];
-    x[i] = __fadd_rn(a, b);
-    x[i + 1] = __fsub_rn(a, b);
-  }
+  for (int hl = 1; hl < NP; hl <<= 1) {
 #pragma unroll
-  for (int len = 2; len < EPL; len <<= 1) {
+    for (int i = 0; i < NP; i += (hl << 1)) {
 #pragma unroll
-    for (int i = 0; i < EPL; i += (len << 1)) {
-#pragma unroll
-      for (int j = 0; j < len; j += 2) butterfly2(x[i + j], x[i + j + 1], x[i + j + len], x[i + j + len + 1]);
+      for (int j = 0; j < hl; ++j) {
+        const unsigned long long lo = xp[i + j], hi = xp[i + j + hl];
+        xp[i + j] = addp(lo, hi);
+        xp[i + j + hl] = subp(lo, hi);
+      }
     }
   }
   // stages len = EPL and 2*EPL pair this lane with the lanes 8 and 16 away: the
@@ -334,22 +355,13 @@ __device__ __forceinline__ void quantize_quarter(float (&x)[P / 4], float norm, 
     const float sgn = (lane & m) ? -1.0f : 1.0f;
     const unsigned long long sgn2 = pack2(sgn, sgn);
 #pragma unroll
-    for (int i = 0; i < EPL; i += 2) {
-      const float o0 = __shfl_xor_sync(0xffffffffu, x[i], m), o1 = __shfl_xor_sync(0xffffffffu, x[i + 1], m);
-      unsigned long long r;
-      asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(pack2(x[i], x[i + 1])), "l"(sgn2), "l"(pack2(o0, o1)));
-      unpack2(r, x[i], x[i + 1]);
-    }
+    for (int i = 0; i < NP; ++i) xp[i] = fmap(xp[i], sgn2, __shfl_xor_sync(0xffffffffu, xp[i], m));
   }
   // x * (1/sqrt p) [core/fwht.cpp:60-65]  then * sqrt p [core/quantizer.cpp:73-75]
-  const float sq = __fsqrt_rn((float)P);
-  const float isq = __fdiv_rn(1.0f, sq);
   const unsigned long long sq2 = pack2(sq, sq), isq2 = pack2(isq, isq);
+  float x[EPL];
 #pragma unroll
-  for (int i = 0; i < EPL; i += 2) {
-    mul2(x[i], x[i + 1], isq2);
-    mul2(x[i], x[i + 1], sq2);
-  }
+  for (int i = 0; i < NP; ++i) unpack2(mulp(mulp(xp[i], isq2), sq2), x[2 * i], x[2 * i + 1]);
   if constexpr (BITS == 3) { // 8 indices -> 3 bytes, big-endian bit order
     uint32_t r[EPL / 8];
 #pragma unroll
@@ -380,7 +392,7 @@ __device__ __forceinline__ void quantize_quarter(float (&x)[P / 4], float norm, 
 }
 
 template <int P, int BITS>
-__global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const AppendLaunch a) {
+__global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kernel(const AppendLaunch a) {
   constexpr int EPL = P / 4;     // coordinates per lane
   constexpr int PITCH = P + 4;   // floats; +16 B keeps both passes' 128-bit reads conflict-free
   constexpr int QB = BITS == 16 ? 4 : BITS;
@@ -389,14 +401,14 @@ __global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const Append
   float *redo_buf = tile + (size_t)AT_TILE * PITCH; // (AT_THREADS/32) x P floats for the general routine
   __shared__ __align__(8) uint64_t bar;
   __shared__ __align__(16) uint2 qtab[QT_ENTRIES];
-  __shared__ float s_norm[AT_TILE];
-  __shared__ int redo_count;
-  __shared__ int redo_list[AT_TILE];
+  __shared__ float2 s_norm[AT_TILE]; // (norm, 1/norm); norm < 0 marks a vector not handled here
+  __shared__ int redo_count[2];          // alternates with the tile parity
+  __shared__ int redo_list[2][AT_TILE];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int vt = warp * 8 + (lane & 7); // vector of the tile this lane works on in pass 2
   const int part = lane >> 3;           // which quarter of it
-  if constexpr (BITS != 16) build_quant_table<QB>(qtab, tid);
+  if constexpr (BITS != 16) build_quant_table<QB>(qtab, tid, AT_THREADS);
   const uint32_t qtab_addr = smem_u32(qtab);
   const CacheView &c = a.c;
   const long long n_items = (long long)a.heads_in_call * a.n_tokens;
@@ -407,7 +419,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const Append
   if (tid == 0) {
     mbar_init(&bar, AT_TILE);
     fence_barrier_init();
-    redo_count = 0;
+    redo_count[0] = redo_count[1] = 0;
   }
   if (tid < AT_TILE) // zero the padding columns once (dim < P); bulk copies never touch them
     for (int i = dim; i < P; ++i) tile[(size_t)tid * PITCH + i] = 0.f;
@@ -430,10 +442,13 @@ __global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const Append
   if (tile_idx < n_tiles && tid < AT_TILE) issue(tile_idx);
   uint32_t parity = 0;
   for (; tile_idx < n_tiles; tile_idx += gridDim.x) {
-    if (!mbar_wait(&bar, parity)) {
-      if (tid == 0) atomicExch(a.status, 1);
-      return;
+    // Only the pass-1 warps poll the copy barrier; everyone else learns of the data
+    // through the block barrier after pass 1 (a failed wait is flagged, not fatal:
+    // all threads must still reach the barriers).
+    if (tid < AT_TILE) {
+      if (!mbar_wait(&bar, parity) && tid == 0) atomicExch(a.status, 1);
     }
+    const uint32_t par = parity; // this tile's slot in the redo bookkeeping
     parity ^= 1u;
 
     // ---- pass 1: sequential norms (core/quantizer.cpp:59-66), one thread per vector ----
@@ -442,14 +457,14 @@ __global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const Append
       bool live = false;
       if (g < n_items) live = place_item32(a, (uint32_t)g).store;
       if (live) {
-        const float4 *r4 = reinterpret_cast<const float4 *>(tile + (size_t)tid * PITCH);
+        const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(tile + (size_t)tid * PITCH);
         float sum = 0.f;
 #pragma unroll 8
         for (int i = 0; i < P / 4; ++i) {
-          const float4 v = r4[i];
-          float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
-          mul2(s0, s1, pack2(v.x, v.y));
-          mul2(s2, s3, pack2(v.z, v.w));
+          const ulonglong2 v = r2[i];
+          float s0, s1, s2, s3;
+          unpack2(mulp(v.x, v.x), s0, s1);
+          unpack2(mulp(v.y, v.y), s2, s3);
           sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, s0), s1), s2), s3);
         }
         const bool all_zero = sum == 0.f;
@@ -457,10 +472,10 @@ __global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const Append
         // norm >= 1e-5 makes the +-3 sigma clip a no-op and rules out NaN (see
         // quantize_lookup); an all-zero vector quantises to the middle index either way
         const bool plain = (norm >= 1e-5f && norm < INFINITY) || all_zero;
-        s_norm[tid] = plain ? norm : -1.f;
-        if (!plain) redo_list[atomicAdd(&redo_count, 1)] = tid;
+        s_norm[tid] = plain ? make_float2(norm, __fdiv_rn(1.0f, norm)) : make_float2(-1.f, 1.f);
+        if (!plain) redo_list[par][atomicAdd(&redo_count[par], 1)] = tid;
       } else {
-        s_norm[tid] = -1.f;
+        s_norm[tid] = make_float2(-1.f, 1.f);
       }
     }
 
@@ -469,37 +484,54 @@ __global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const Append
     ItemPlace p;
     p.store = p.mirror = false;
     if (g < n_items) p = place_item32(a, (uint32_t)g);
-    float x[EPL];
-    {
-      const bool have = p.store || p.mirror;
-      const float4 *r4 = reinterpret_cast<const float4 *>(tile + (size_t)vt * PITCH + part * EPL);
-#pragma unroll
-      for (int i = 0; i < EPL / 4; ++i) {
-        const float4 v = have ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+    __syncthreads(); // the tile has landed (seen by the pass-1 warps) and the norms are published
+    if constexpr (BITS != 16) {
+      const int n_redo = redo_count[par];
+      if (tid == 0) redo_count[par ^ 1u] = 0; // the other slot was last read before the previous tile's second barrier
+      if (n_redo > 0) { // rare: tiny, infinite or NaN norms go through the general routine (it reads the source again)
+        for (int e = warp; e < n_redo; e += AT_THREADS / 32)
+          append_item_general(a, tile_idx * AT_TILE + redo_list[par][e], redo_buf + (size_t)warp * P, lane);
       }
     }
-    __syncthreads(); // rows are in registers, norms are published; the tile buffer is free
-    const float norm = BITS == 16 ? 1.f : s_norm[vt];
+    // Vectors that pass 1 handed to the general routine (norm < 0) are skipped here
+    // altogether: their lanes run the transform on zeros, because the table
+    // quantiser's address arithmetic is only defined for the finite, normalised
+    // values of the vectors pass 1 accepted.
+    const float2 nrm = BITS == 16 ? make_float2(1.f, 1.f) : s_norm[vt];
+    const float norm = nrm.x;
+    const bool skip = BITS != 16 && norm < 0.f;
+    if (skip) p.store = p.mirror = false;
+    unsigned long long xp[EPL / 2]; // coordinates (2i, 2i+1) of this quarter, packed
+    {
+      const bool have = p.store || p.mirror;
+      const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(tile + (size_t)vt * PITCH + part * EPL);
+#pragma unroll
+      for (int i = 0; i < EPL / 4; ++i) {
+        const ulonglong2 v = have ? r2[i] : make_ulonglong2(0ull, 0ull);
+        xp[2 * i] = v.x;
+        xp[2 * i + 1] = v.y;
+      }
+    }
+    __syncthreads(); // every quarter is in registers; the tile buffer is free
     const long long next = tile_idx + gridDim.x;
     if (next < n_tiles && tid < AT_TILE) {
       fence_proxy_async();
       issue(next);
     }
     if (p.mirror) {
-      float4 *m4 = reinterpret_cast<float4 *>(c.mirror + (size_t)p.h * c.mirror_stride + (size_t)p.slot * 2 * dim +
-                                              (a.which ? dim : 0) + part * EPL);
+      ulonglong2 *m2 = reinterpret_cast<ulonglong2 *>(c.mirror + (size_t)p.h * c.mirror_stride +
+                                                      (size_t)p.slot * 2 * dim + (a.which ? dim : 0) + part * EPL);
 #pragma unroll
       for (int i = 0; i < EPL / 4; ++i)
-        if (part * EPL + 4 * i < dim) m4[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+        if (part * EPL + 4 * i < dim) m2[i] = make_ulonglong2(xp[2 * i], xp[2 * i + 1]);
     }
     if constexpr (BITS == 16) {
       if (p.store) {
         uint8_t *slab = a.which ? c.v_slab : c.k_slab;
         const size_t stride = a.which ? c.v_stride : c.k_stride;
-        float4 *dst = reinterpret_cast<float4 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4)) + part * (EPL / 4);
+        ulonglong2 *dst = reinterpret_cast<ulonglong2 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4)) + part * (EPL / 4);
 #pragma unroll
-        for (int i = 0; i < EPL / 4; ++i) dst[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+        for (int i = 0; i < EPL / 4; ++i) dst[i] = make_ulonglong2(xp[2 * i], xp[2 * i + 1]);
         if (part == 0) ((a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = 1.0f;
       }
     } else {
@@ -507,29 +539,19 @@ __global__ void __launch_bounds__(AT_THREADS, 2) append_tile_kernel(const Append
       // vector is not stored here -- ragged tile end, or a vector left to the general
       // routine -- work on zeros and skip the store.
       constexpr int NBYTES = EPL * BITS / 8;
-      const bool keep = p.store && norm >= 0.f;
+      const bool keep = p.store;
       uint32_t sgw = 0; // sign bits of this quarter in bits 0..EPL-1
       if (keep) {
         sgw = c.signs[(size_t)p.h * c.sign_words + ((part * EPL) >> 5)];
         if constexpr (EPL < 32) sgw >>= (part * EPL) & 31;
       }
       uint32_t w[(EPL * BITS + 31) / 32];
-      quantize_quarter<P, BITS>(x, keep ? norm : 1.f, sgw, lane, w, qtab_addr);
+      quantize_quarter<P, BITS>(xp, keep ? nrm.y : 1.f, a.sqrt_p, a.inv_sqrt_p, sgw, lane, w, qtab_addr);
       if (keep) {
         uint8_t *slab = a.which ? c.v_slab : c.k_slab;
         const size_t stride = a.which ? c.v_stride : c.k_stride;
         store_packed<NBYTES>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * BITS / 8) + part * NBYTES, w);
         if (part == 0) ((a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = norm;
-      }
-    }
-    if constexpr (BITS != 16) {
-      __syncthreads();
-      const int n_redo = redo_count;
-      if (n_redo > 0) { // rare: tiny, infinite or NaN norms
-        for (int e = warp; e < n_redo; e += AT_THREADS / 32)
-          append_item_general(a, tile_idx * AT_TILE + redo_list[e], redo_buf + (size_t)warp * P, lane);
-        __syncthreads();
-        if (tid == 0) redo_count = 0;
       }
     }
   }

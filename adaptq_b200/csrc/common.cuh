@@ -186,14 +186,14 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 // Returns false if the phase did not complete within the spin budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
+  for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(20000u) /* suspend-time hint, ns: fewer polling rounds */
         : "memory");
     if (done) return true;
   }

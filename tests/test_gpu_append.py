@@ -96,6 +96,37 @@ def test_special_values(gpu_lib, orc):
         assert same.all()
 
 
+def test_special_rows_inside_a_bulk_batch(gpu_lib, orc):
+    """NaN / Inf / huge / tiny / zero vectors scattered through a 700-token batch:
+    they take the general routine while their warp neighbours take the table
+    quantiser; every row must still equal the oracle's."""
+    from adaptq_b200 import MHAContext
+    heads, dim, T = 2, 128, 700
+    rng = np.random.default_rng(77)
+    k, v = make_kv(rng, T, heads, dim, "normal_outlier")
+    for a in (k, v):
+        for t in rng.choice(T, 60, replace=False):
+            kind = rng.integers(0, 6)
+            h = rng.integers(0, heads)
+            if kind == 0: a[t, h] = 0.0
+            elif kind == 1: a[t, h, rng.integers(0, dim)] = np.nan
+            elif kind == 2: a[t, h, rng.integers(0, dim)] = np.inf
+            elif kind == 3: a[t, h] = 3e37
+            elif kind == 4: a[t, h] *= 1e-9
+            else: a[t, h] = 1e-30
+    for bits in (2, 3, 4):
+        ctx = MHAContext(heads, dim, bits, bits, T, seed=5, v_mass=0.0, hybrid_thresh=0)
+        cpu = CpuHeads(orc, heads, dim, bits, bits, T, 5)
+        ctx.append_all(k, v)
+        cpu.append_many(k, v)
+        ctx.synchronize()
+        for h in range(heads):
+            e = ctx.export_head(h)
+            assert (e["k_rows"] == cpu.heads[h].k_data()).all() and (e["v_rows"] == cpu.heads[h].v_data()).all()
+            for got, want in ((e["k_scale"], cpu.heads[h].k_scale()), (e["v_scale"], cpu.heads[h].v_scale())):
+                assert ((got.view(np.uint32) == want.view(np.uint32)) | (np.isnan(got) & np.isnan(want))).all()
+
+
 def test_general_and_specialised_append_agree(gpu_lib, orc):
     """Policy 1 forces the general (warp-per-vector) kernel; bytes must not change."""
     from adaptq_b200 import MHAContext

@@ -39,6 +39,10 @@ if ROOT not in sys.path:
 SEQS, LAYERS, KV_HEADS, DIM, CONTEXT = 256, 32, 8, 128, 8192
 K_BITS, V_BITS = 4, 2
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes (read + write) per algorithmic byte of the streaming decode kernel, from the ncu
+# capture summarised in profiles/compute_stream_kernel_k4v2_dim128_ctx8192.md (1024 heads:
+# 889.4 MB moved for 873.5 MB algorithmic); traffic grows in proportion to the heads processed.
+STREAM_TRAFFIC_PER_ALG_BYTE = 1.018
 
 
 def parse():
@@ -49,8 +53,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS, help="sequences per GPU (default: the BASELINE config)")
     ap.add_argument("--context", type=int, default=CONTEXT)
-    ap.add_argument("--mode", default="decode", choices=["decode", "append"],
-                    help="append: run only the bulk-append kernel benchmark and print its JSON")
+    ap.add_argument("--mode", default="decode", choices=["decode", "append", "latency"],
+                    help="append: only the bulk-append kernel benchmark; latency: per-token decode latency of the "
+                         "small per-layer configurations (BASELINE configs[0..2])")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-append-bench", action="store_true")
     ap.add_argument("--cpu-sample-heads", type=int, default=0)
@@ -239,6 +244,54 @@ def append_bench(torch, L, peak):
                         "larger than L2)", "results": out}
 
 
+def latency_bench(torch):
+    """Per-token decode latency of the small configurations: one engine per layer
+    (seed 42 ^ layer), per step and layer one append of the new token and one
+    attention call, device tensors in place.  These shapes move 0.5-25 MB per
+    step, so they are launch/latency bound; the figure of merit is us per token."""
+    import numpy as np
+    import adaptq_b200
+    out = {}
+    cfgs = [
+        ("config0_engine_d64_h4_k4v2_ctx2048_dense", 1, 4, 64, 2048, 2048, [(4, 2)], 0.0, 0, "normal"),
+        ("config0_engine_defaults_sparse_v", 1, 4, 64, 2048, 2048, [(4, 2)], 0.95, 512, "normal"),
+        ("config1_qwen2_0.5b_24x14_d64_ctx1024", 24, 14, 64, 1024, 1152, [(16, 2)] + [(4, 2)] * 23, 0.0, 0, "student4"),
+        ("config2_tinyllama_22x4_d64_ctx2048", 22, 4, 64, 2048, 2304, [(16, 2)] + [(3, 2)] * 21, 0.0, 0, "normal"),
+    ]
+    g = torch.Generator(device="cuda").manual_seed(7)
+    for name, layers, heads, dim, ctx_len, cap, bits, v_mass, hyb, dist in cfgs:
+        engines = [adaptq_b200.MHAContext(heads, dim, bits[l][0], bits[l][1], cap, seed=42 ^ l, v_mass=v_mass,
+                                          hybrid_thresh=hyb) for l in range(layers)]
+        for e in engines:
+            k = torch.randn((ctx_len, heads, dim), device="cuda", generator=g)
+            v = torch.randn((ctx_len, heads, dim), device="cuda", generator=g)
+            if dist == "student4":  # heavy tails, crude stand-in: normal / sqrt(chi2/4)
+                k = k / torch.sqrt(torch.randn((ctx_len, heads, dim, 4), device="cuda", generator=g).pow(2).mean(-1))
+            e.append_all(k, v)
+        kn = torch.randn((layers, heads, dim), device="cuda", generator=g)
+        q = torch.randn((layers, heads, dim), device="cuda", generator=g)
+        o = torch.empty((layers, heads, dim), device="cuda")
+
+        def step():
+            for l, e in enumerate(engines):
+                e.append_all(kn[l], kn[l])
+                e.compute_all(q[l], out=o[l])
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+        steps = 50
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / steps
+        out[name] = {"us_per_token": dt * 1e6, "us_per_layer": dt * 1e6 / layers, "layers": layers, "heads": heads,
+                     "context": ctx_len, "tokens_per_s": 1.0 / dt}
+        for e in engines:
+            e.close()
+    return out
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -257,6 +310,10 @@ def run_ours(args):
     if args.mode == "append":
         if rank == 0:
             print(json.dumps({"metric": "bulk_append_vectors_per_s", "append": append_bench(torch, L, peak)}))
+        return
+    if args.mode == "latency":
+        if rank == 0:
+            print(json.dumps({"metric": "decode_latency_us_per_token", "latency": latency_bench(torch)}))
         return
 
     heads = args.seqs * LAYERS * KV_HEADS
@@ -334,7 +391,9 @@ def run_ours(args):
     kt = sum(kern_ms) / len(kern_ms) / 1e3
     roof = {"bound": "hbm", "kernel": "compute_stream_kernel<K4,V2,dim128>", "achieved": alg_bytes / kt / 1e9,
             "peak": peak, "unit": "GB/s", "frac": alg_bytes / kt / 1e9 / peak, "peak_source": peak_src,
-            "traffic": None, "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kt * 1e3,
+            "traffic": alg_bytes * STREAM_TRAFFIC_PER_ALG_BYTE,
+            "traffic_source": "ncu dram__bytes_read+write on a 1024-head launch, scaled by heads (profiles/)",
+            "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kt * 1e3,
             "of_nominal_8TBs": alg_bytes / kt / 8e12}
 
     line = {"metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,

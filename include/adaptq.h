@@ -73,8 +73,8 @@ void adaptq_append(adaptq_ctx_t ctx, const float *key, const float *val,
  * cache, out zeroed), -1 on a NULL argument. */
 int adaptq_compute(adaptq_ctx_t ctx, const float *query, float *out);
 
-/* [h:75 c:109]  queries, outs: float[num_queries*dim].  The cache is read
- * once for all queries. */
+/* [h:75 c:109]  queries, outs: float[num_queries*dim].  One launch serves all
+ * queries; the cache comes from HBM once (re-reads are served by L2). */
 int adaptq_compute_batch(adaptq_ctx_t ctx, const float *queries,
                          int num_queries, float *outs);
 

@@ -39,8 +39,10 @@ int adaptq_mha_append_batch(adaptq_mha_t mha, const float *keys,
 
 /* Attention for every head, queries_per_head queries each.  queries, outs:
  * float [n_heads][queries_per_head][dim].  Equals adaptq_mha_compute_batch
- * on every head (upstream attention/attention.cpp:480-677); the cache is
- * read once per head.  Returns the largest per-head token count. */
+ * on every head (upstream attention/attention.cpp:480-677).  The queries of
+ * a head are processed side by side, so the head's cache comes from HBM
+ * once and the other queries find it in L2.  Returns the largest per-head
+ * token count. */
 int adaptq_mha_compute_all(adaptq_mha_t mha, const float *queries,
                            int queries_per_head, float *outs);
 

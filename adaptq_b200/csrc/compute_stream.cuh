@@ -28,7 +28,13 @@
 //    2^30): integer shared-memory reductions are native and order-independent,
 //    so the result is deterministic; floating-point ones are not native;
 //  * one inverse Walsh-Hadamard transform at the end (or in the merge kernel
-//    when the sequence is split).
+//    when the sequence is split);
+//  * a helper warp works one item ahead and one item behind the consumers: it
+//    rotates the next item's query while the current item streams, and it
+//    finishes an item (normalise, inverse transform, store) after the consumers
+//    have moved on, so neither step sits between two items' streams.  A block
+//    walks a contiguous run of items; consecutive spans of one (head, query)
+//    reuse the K table.
 //
 // No tensor cores: the path is ~5 FLOP/byte of irregular table work.
 #pragma once
@@ -36,9 +42,6 @@
 
 #ifndef AQ_COMPACT_BUCKETS
 #define AQ_COMPACT_BUCKETS 1
-#endif
-#ifndef AQ_PACKED_ADD
-#define AQ_PACKED_ADD 1
 #endif
 
 namespace aq {
@@ -56,13 +59,15 @@ namespace aq {
 
 constexpr int CS_CONSUMERS = 512;           // 16 consumer warps
 constexpr int CS_WARPS = CS_CONSUMERS / 32;
-constexpr int CS_THREADS = CS_CONSUMERS + 32; // + 1 producer warp
+constexpr int CS_HELPER_TID = CS_CONSUMERS + 32;
+constexpr int CS_THREADS = CS_CONSUMERS + 64; // + producer warp + helper warp
+constexpr int CS_MISC_BYTES = 3072;
 constexpr int CS_STAGE_BYTES = 16384;
 constexpr int CS_MAX_STAGES = 6;             // ring stages: as many as fit beside the tables (3..5)
 constexpr int CS_SPAN_MAX = 8192;           // tokens per work item (scores kept in shared memory)
 constexpr int CS_TABLE_BYTES = 65536;       // [256][64] floats
 constexpr size_t CS_SMEM_BYTES = 65536 /* alignment slack, holds the ring */ + CS_TABLE_BYTES /* K table */ +
-                                 CS_TABLE_BYTES /* V buckets */ + CS_SPAN_MAX * 4 /* scores */ + 2048 /* misc */;
+                                 CS_TABLE_BYTES /* V buckets */ + CS_SPAN_MAX * 4 /* scores */ + CS_MISC_BYTES;
 
 struct StreamLaunch {
   CacheView c;
@@ -90,42 +95,29 @@ __device__ __forceinline__ void red_shared_add(uint32_t addr, uint32_t v) {
   asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ float consumer_reduce(float v, float *red, bool is_max) {
+// Block-wide reductions over the consumer threads with ONE barrier each.  The
+// max and the sums use different arrays and alternate within an item, so an
+// array is rewritten only after a later barrier has passed every reader.
+__device__ __forceinline__ float consumer_max(float v, float *red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  v = is_max ? warp_max(v) : warp_sum(v);
-  consumer_sync();
+  v = warp_max(v);
   if (lane == 0) red[warp] = v;
   consumer_sync();
   float r = red[0];
 #pragma unroll
-  for (int i = 1; i < CS_WARPS; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+  for (int i = 1; i < CS_WARPS; ++i) r = fmaxf(r, red[i]);
   return r;
 }
-
-// Sum two values over all consumer threads at once.
-__device__ __forceinline__ void consumer_reduce2(float &a, float &b, float *red) {
+__device__ __forceinline__ void consumer_sum2(float &a, float &b, float *red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   a = warp_sum(a);
   b = warp_sum(b);
-  consumer_sync();
   if (lane == 0) { red[warp] = a; red[32 + warp] = b; }
   consumer_sync();
   a = red[0];
   b = red[32];
 #pragma unroll
   for (int i = 1; i < CS_WARPS; ++i) { a += red[i]; b += red[32 + i]; }
-}
-
-__device__ __forceinline__ void consumer_butterflies(float *x, int p) {
-  for (int len = 1; len < p; len <<= 1) {
-    for (int t = threadIdx.x; t < (p >> 1); t += CS_CONSUMERS) {
-      int i = ((t / len) * (len << 1)) + (t % len);
-      float a = x[i], b = x[i + len];
-      x[i] = a + b;
-      x[i + len] = a - b;
-    }
-    consumer_sync();
-  }
 }
 
 // Walsh-Hadamard butterflies over P = 32*EPL values held EPL per lane (lane l
@@ -208,18 +200,42 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   uint32_t *bucket = reinterpret_cast<uint32_t *>(table_p + CS_TABLE_BYTES);
   float *sc = reinterpret_cast<float *>(table_p + CS_TABLE_BYTES + BUCKET_BYTES);
   unsigned char *misc = reinterpret_cast<unsigned char *>(sc + CS_SPAN_MAX);
-  float *qr = reinterpret_cast<float *>(misc);          // P floats (<= 512 B)
-  float *red = qr + 128;                                 // 64 floats
-  float *s_cb = red + 64;                                // 16 floats: V centroids
+  constexpr int ACC_PITCH = 132;                         // P accumulators + running max + sum
+  float *qrot = reinterpret_cast<float *>(misc);         // 2 x 128: rotated queries, double-buffered
+  float *accb = qrot + 256;                              // 2 x ACC_PITCH: finished items for the helper warp
+  float *red_max = accb + 2 * ACC_PITCH;                 // 32 floats
+  float *red_sum = red_max + 32;                         // 64 floats
+  float *s_cb = red_sum + 64;                            // 16 floats: V centroids
   uint64_t *full = reinterpret_cast<uint64_t *>(s_cb + 16);
   uint64_t *empty = full + CS_MAX_STAGES;
-  int *s_fail = reinterpret_cast<int *>(empty + CS_MAX_STAGES);
+  uint64_t *qfull = empty + CS_MAX_STAGES;               // [2] rotated query written / table built from it
+  uint64_t *qempty = qfull + 2;
+  uint64_t *afull = qempty + 2;                          // [2] accumulator handed over / stored
+  uint64_t *aempty = afull + 2;
+  int *s_fail = reinterpret_cast<int *>(aempty + 2);
   // The ring lives in whatever is left: the slack in front of the 64 KB-aligned
   // table and the tail behind the misc block.
-  unsigned char *back = misc + 2048;
-  const int n_front = min((int)(front / CS_STAGE_BYTES), CS_MAX_STAGES);
-  const int n_back = (int)((CS_SMEM_BYTES - front - CS_TABLE_BYTES - BUCKET_BYTES - CS_SPAN_MAX * 4 - 2048) / CS_STAGE_BYTES);
-  const int n_stages = min(n_front + n_back, CS_MAX_STAGES);
+  unsigned char *back = misc + CS_MISC_BYTES;
+  const int back_bytes = (int)(CS_SMEM_BYTES - front - CS_TABLE_BYTES - BUCKET_BYTES - CS_SPAN_MAX * 4 - CS_MISC_BYTES);
+  int n_front = min((int)(front / CS_STAGE_BYTES), CS_MAX_STAGES);
+  int n_back = min(back_bytes / CS_STAGE_BYTES, CS_MAX_STAGES - n_front);
+  // Each K stage comes with its tokens' K scales (a second bulk copy on the same
+  // barrier).  They go into what the stages leave over, or take a stage's place.
+  constexpr int KS_STAGE_BYTES = TKN * 4;
+  constexpr int KS_AREA_BYTES = CS_MAX_STAGES * KS_STAGE_BYTES;
+  unsigned char *ks_area;
+  if ((int)front - n_front * CS_STAGE_BYTES >= KS_AREA_BYTES) {
+    ks_area = smem + (size_t)n_front * CS_STAGE_BYTES;
+  } else if (back_bytes - n_back * CS_STAGE_BYTES >= KS_AREA_BYTES) {
+    ks_area = back + (size_t)n_back * CS_STAGE_BYTES;
+  } else if (n_back > 0) {
+    --n_back;
+    ks_area = back + (size_t)n_back * CS_STAGE_BYTES;
+  } else {
+    n_front = max(n_front - 1, 0);
+    ks_area = smem + (size_t)n_front * CS_STAGE_BYTES;
+  }
+  const int n_stages = n_front + n_back;
   const bool layout_ok = n_stages >= 2;
   auto stage_ptr = [&](int s) -> unsigned char * {
     return s < n_front ? smem + (size_t)s * CS_STAGE_BYTES : back + (size_t)(s - n_front) * CS_STAGE_BYTES;
@@ -230,11 +246,21 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   const int dim = c.dim;
   const int items_base = a.heads_in_call * a.nq;
   const int n_items = items_base * a.n_splits;
+  // A block owns a contiguous run of items, so the spans of one (head, query)
+  // follow each other and share the query rotation and the K table.
+  const int item_begin = (int)((long long)blockIdx.x * n_items / gridDim.x);
+  const int item_end = (int)((long long)(blockIdx.x + 1) * n_items / gridDim.x);
 
   if (tid == 0) {
     for (int s = 0; s < CS_MAX_STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], CS_WARPS);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qfull[s], 1);
+      mbar_init(&qempty[s], 1);
+      mbar_init(&afull[s], P / 32);
+      mbar_init(&aempty[s], 1);
     }
     *s_fail = layout_ok ? 0 : 2;
     for (int i = 0; i < 16; ++i) s_cb[i] = c_cb[VB - 2][i];
@@ -246,17 +272,30 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     return;
   }
 
+  // Every wait in this kernel is bounded; a wait that gives up raises the
+  // block's failure flag, after which all later waits are skipped and the
+  // block drains (the host reads the status word and reports the call as failed).
+  auto guarded_wait = [&](uint64_t *bar, uint32_t parity) {
+    if (*reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(bar, parity)) {
+      *reinterpret_cast<volatile int *>(s_fail) = 1;
+      atomicExch(a.status, 1);
+    }
+  };
+  constexpr int EPL = P / 32; // query / accumulator elements per lane of the helper warp
+  const float isp = 1.f / sqrtf((float)P);
+
   // ======================= producer warp ====================================
-  if (tid >= CS_CONSUMERS) {
+  if (tid >= CS_CONSUMERS && tid < CS_HELPER_TID) {
     if (tid != CS_CONSUMERS) return;
     int stage = 0;
     uint32_t phase = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int item = item_begin; item < item_end; ++item) {
       const int split = item % a.n_splits, hq = item / a.n_splits;
       const int h = a.head0 + hq / a.nq;
       const int t0 = min(a.n, split * a.span), t1 = min(a.n, t0 + a.span);
       const uint8_t *kb = c.k_slab + (size_t)h * c.k_stride;
       const uint8_t *vb = c.v_slab + (size_t)h * c.v_stride;
+      const float *ksb = c.k_scale + (size_t)h * c.s_stride;
       for (int pass = 0; pass < 2; ++pass) {
         const int rowb = pass ? VROW : KROW, tn = pass ? TVN : TKN;
         const uint8_t *src = pass ? vb : kb;
@@ -265,10 +304,87 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
             *reinterpret_cast<volatile int *>(s_fail) = 1;
             atomicExch(a.status, 1);
           }
-          const uint32_t bytes = ((uint32_t)(min(tn, t1 - t) * rowb) + 15u) & ~15u;
-          mbar_expect_tx(&full[stage], bytes);
+          const int cnt = min(tn, t1 - t);
+          const uint32_t bytes = ((uint32_t)(cnt * rowb) + 15u) & ~15u;
+          // scales: rounded up to 16 bytes; the per-head scale rows carry 128 bytes of padding
+          const uint32_t sbytes = pass ? 0u : (((uint32_t)cnt * 4u + 15u) & ~15u);
+          mbar_expect_tx(&full[stage], bytes + sbytes);
           bulk_g2s(stage_ptr(stage), src + (size_t)t * rowb, bytes, &full[stage]);
+          if (sbytes) bulk_g2s(ks_area + (size_t)stage * KS_STAGE_BYTES, ksb + t, sbytes, &full[stage]);
           if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    return;
+  }
+
+  // ======================= helper warp ======================================
+  // prologue(i): rotate the query of item i (attention.cpp:537-550) into
+  // qrot[buffer] unless item i continues the previous item's (head, query).
+  // epilogue(i): take the finished accumulator of item i, then either store the
+  // split-KV partial or normalise, apply the inverse transform
+  // (core/fwht.cpp:106-134) and store the output.
+  // Order: prologue(first), then for every item prologue(i+1) before epilogue(i).
+  if (tid >= CS_HELPER_TID) {
+    const int lane = tid & 31;
+    int prev_hq = -1, qcount = 0;
+    uint32_t sg_latest = 0;
+    auto prologue = [&](int item) {
+      const int hq = item / a.n_splits;
+      if (hq == prev_hq) return;
+      prev_hq = hq;
+      const float *qp = a.q + (size_t)hq * dim;
+      float v[EPL];
+      float part = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        v[e] = (EPL * lane + e) < dim ? __ldg(qp + EPL * lane + e) : 0.f;
+        part += v[e] * v[e];
+      }
+      const uint32_t sg = __ldg(c.signs + (size_t)(a.head0 + hq / a.nq) * c.sign_words + ((EPL * lane) >> 5));
+      const float qn = sqrtf(warp_sum(part) + 1e-12f);
+      const float inv = 1.f / qn;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[e] = v[e] * inv * (((sg >> ((EPL * lane + e) & 31)) & 1u) ? -1.f : 1.f);
+      warp_butterflies<EPL>(v, lane);
+      const float back = sqrtf((float)P) * qn;
+      const int b = qcount & 1;
+      guarded_wait(&qempty[b], (((uint32_t)qcount >> 1) & 1u) ^ 1u); // the table of two queries ago is built
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) qrot[b * 128 + EPL * lane + e] = v[e] * isp * back;
+      sg_latest = sg;
+      ++qcount;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qfull[b]);
+    };
+    if (item_begin < item_end) prologue(item_begin);
+    for (int item = item_begin, idx = 0; item < item_end; ++item, ++idx) {
+      const uint32_t sg = sg_latest;
+      if (item + 1 < item_end) prologue(item + 1);
+      const int b = idx & 1;
+      guarded_wait(&afull[b], ((uint32_t)idx >> 1) & 1u);
+      const float *ab = accb + b * ACC_PITCH;
+      const int split = item % a.n_splits, hq = item / a.n_splits;
+      float v[EPL];
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[e] = ab[EPL * lane + e];
+      const float mx = ab[P], ls = ab[P + 1];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&aempty[b]); // values are in registers: the slot may be refilled
+      if (a.n_splits > 1 || a.force_partial) {
+        float *pp = a.partial + ((size_t)split * items_base + hq) * (size_t)(2 + P);
+        if (lane == 0) { pp[0] = mx; pp[1] = ls; }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) pp[2 + EPL * lane + e] = v[e];
+      } else {
+        const float invl = 1.f / ls;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) v[e] *= invl;
+        warp_butterflies<EPL>(v, lane);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          const int j = EPL * lane + e;
+          if (j < dim) a.out[(size_t)hq * dim + j] = v[e] * isp * (((sg >> (j & 31)) & 1u) ? -1.f : 1.f);
         }
       }
     }
@@ -305,7 +421,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   }
   float *table = reinterpret_cast<float *>(table_p);
   const float *kcb = c_cb[KB - 2];
-  const float isp = 1.f / sqrtf((float)P);
   const float attn_s = 1.f / (sqrtf((float)dim) * (float)P);
 
   int stage = 0;
@@ -352,62 +467,30 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     if (++stage == n_stages) { stage = 0; phase ^= 1u; }
   };
 
-  constexpr int EPL = P / 32; // query / accumulator elements per lane of warp 0
-  float q_next[EPL];
-  uint32_t sg_next = 0; // the sign word covering this lane's elements (EPL divides 32)
-  if (warp == 0 && (int)blockIdx.x < n_items) {
-    const int hq0 = blockIdx.x / a.n_splits;
-    const float *q0 = a.q + (size_t)hq0 * dim;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) q_next[e] = (EPL * lane + e) < dim ? __ldg(q0 + EPL * lane + e) : 0.f;
-    sg_next = __ldg(c.signs + (size_t)(a.head0 + hq0 / a.nq) * c.sign_words + ((EPL * lane) >> 5));
-  }
-  uint32_t sg_cur = 0;
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  // The buckets start at zero; afterwards the fold that reads a bucket clears it.
+  for (int i = tid; i < BUCKET_BYTES / 4; i += CS_CONSUMERS) bucket[i] = 0u;
+  int prev_hq = -1, quse = 0;
+  for (int item = item_begin, idx = 0; item < item_end; ++item, ++idx) {
     const int split = item % a.n_splits, hq = item / a.n_splits;
     const int hl = hq / a.nq;
     const int h = a.head0 + hl;
     const int t0 = min(a.n, split * a.span), t1 = min(a.n, t0 + a.span);
     const int len = t1 - t0;
-    { // pull this span's K and V scale lines into L2; they are read after the K stream
-      const float *sp = (tid < 256 ? c.k_scale : c.v_scale) + (size_t)h * c.s_stride + t0;
-      const int off = (tid & 255) * 32; // floats; 128-byte lines
+    { // pull this span's V scale lines into L2; they are read after the K stream
+      const float *sp = c.v_scale + (size_t)h * c.s_stride + t0;
+      const int off = tid * 32; // floats; 128-byte lines
       if (off < len) asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + off));
     }
-
-    // ---- rotate the query (attention.cpp:537-550): warp 0, in registers; the other
-    // warps clear the buckets meanwhile ------------------------------------------------
-    if (warp == 0) {
-      float v[EPL];
-      float part = 0.f;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        v[e] = q_next[e];
-        part += v[e] * v[e];
-      }
-      sg_cur = sg_next;
-      { // fetch the next item's query and signs now; they are consumed one iteration later
-        const int nitem = item + gridDim.x;
-        if (nitem < n_items) {
-          const int nhq = nitem / a.n_splits;
-          const float *qn_ptr = a.q + (size_t)nhq * dim;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) q_next[e] = (EPL * lane + e) < dim ? __ldg(qn_ptr + EPL * lane + e) : 0.f;
-          sg_next = __ldg(c.signs + (size_t)(a.head0 + nhq / a.nq) * c.sign_words + ((EPL * lane) >> 5));
-        }
-      }
-      const float qn = sqrtf(warp_sum(part) + 1e-12f);
-      const float inv = 1.f / qn;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) v[e] = v[e] * inv * (((sg_cur >> ((EPL * lane + e) & 31)) & 1u) ? -1.f : 1.f);
-      warp_butterflies<EPL>(v, lane);
-      const float back = sqrtf((float)P) * qn;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) qr[EPL * lane + e] = v[e] * isp * back;
+    if (hq == prev_hq) {
+      // same (head, query) as the previous item: the table stands.  The barrier keeps
+      // this item's score writes behind the last fold reads of the previous item.
+      consumer_sync();
     } else {
-      for (int i = tid - 32; i < BUCKET_BYTES / 4; i += CS_CONSUMERS - 32) bucket[i] = 0u;
-    }
-    consumer_sync();
+    prev_hq = hq;
+    const int qb = quse & 1;
+    guarded_wait(&qfull[qb], ((uint32_t)quse >> 1) & 1u);
+    ++quse;
+    const float *qr = qrot + qb * 128;
     // ---- build the K byte table ----------------------------------------------------
     {
       // thread -> column (consecutive lanes, consecutive banks), a slice of the byte values
@@ -442,6 +525,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       }
     }
     consumer_sync();
+    if (tid == 0) mbar_arrive(&qempty[qb]); // every thread has read the rotated query
+    }
 
     AQ_MARK(0)
 #ifdef AQ_PROBE
@@ -449,9 +534,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #endif
     // ---- K stream: logits into sc[] ----------------------------------------------------
     // After the group reduction one lane per token owns its dot product; that lane
-    // also fetches the token's K scale (early, so the load overlaps the tile) and
-    // keeps a running maximum, so no separate scaling pass is needed.
-    const float *ksc = c.k_scale + (size_t)h * c.s_stride + t0;
+    // also reads the token's K scale (it arrived with the stage) and keeps a running
+    // maximum, so no separate scaling pass is needed.
     const float *vsc = c.v_scale + (size_t)h * c.s_stride + t0;
     const int own_tok = warp * (TKN / CS_WARPS) + 4 * (KSTEPS == 8 ? wl : (wl >> 1)) + tq;
     const bool owner = KSTEPS == 8 || (wl & 1) == 0;
@@ -460,7 +544,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       wait_full();
       const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
       const bool own_valid = owner && t + own_tok < t1;
-      const float ksv = own_valid ? __ldg(ksc + (t - t0) + own_tok) : 0.f;
+      const float ksv = own_valid ? reinterpret_cast<const float *>(ks_area + (size_t)stage * KS_STAGE_BYTES)[own_tok] : 0.f;
       uint32_t dk[KSTEPS][KWPL];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
@@ -472,23 +556,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       float pv[KSTEPS];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
-#if AQ_PACKED_ADD
-        unsigned long long acc2 = 0ull; // two running sums, added with one f32x2 instruction
-#pragma unroll
-        for (int m = 0; m < KWPL; ++m) {
-          const uint32_t d = dk[s][m];
-#pragma unroll
-          for (int k = 0; k < 4; k += 2) {
-            const float e0 = lds_f32(__byte_perm(d, kconst[m][k], ksel[k]));
-            const float e1 = lds_f32(__byte_perm(d, kconst[m][k + 1], ksel[k + 1]));
-            unsigned long long e2;
-            asm("mov.b64 %0, {%1, %2};" : "=l"(e2) : "f"(e0), "f"(e1));
-            asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc2) : "l"(e2));
-          }
-        }
-        float a0, a1;
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc2));
-#else
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
         for (int m = 0; m < KWPL; ++m) {
@@ -498,7 +565,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
           a0 += lds_f32(__byte_perm(d, kconst[m][2], ksel[2]));
           a1 += lds_f32(__byte_perm(d, kconst[m][3], ksel[3]));
         }
-#endif
         pv[s] = a0 + a1;
       }
       const float total = group_transpose_sum<KSTEPS>(pv, wl);
@@ -522,7 +588,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       vv[r] = i < len ? __ldg(vsc + i) : 0.f;
     }
     AQ_MARK(1)
-    const float mx = consumer_reduce(lane_max, red, true); // its barriers also publish sc[]
+    const float mx = consumer_max(lane_max, red_max); // its barrier also publishes sc[]
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
       const int i = tid + r * CS_CONSUMERS;
@@ -536,17 +602,23 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       sv[r] = e * vv[r] * isp;
       wsum += sv[r];
     }
-    consumer_reduce2(ls, wsum, red);
+    consumer_sum2(ls, wsum, red_sum);
     // weights -> 32-bit fixed point with the span's total mapped to 2^30, so no
     // bucket can overflow and the rounding error is below 2^-31 of the total per token
     const float fx = (wsum > 0.f && wsum < INFINITY) ? 1073741824.0f / wsum : 0.f;
     const float inv_fx = fx > 0.f ? wsum * (1.0f / 1073741824.0f) : 0.f;
     uint32_t *scu = reinterpret_cast<uint32_t *>(sc);
     const int len_pad = min(CS_SPAN_MAX, (len + TVN - 1) / TVN * TVN);
+    // Stored in the order the V stream reads them: the VSTEPS weights that one lane
+    // needs from a tile (tokens 4s + tq of its warp's slice) sit side by side, so the
+    // lane fetches them with 128-bit loads.
+    constexpr int TPWV = TVN / CS_WARPS;
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
       const int i = tid + r * CS_CONSUMERS;
-      if (i < len_pad) scu[i] = __float2uint_rn(sv[r] * fx);
+      const int rem = i % TPWV;
+      const int pos = i - rem + (rem & 3) * VSTEPS + (rem >> 2);
+      if (i < len_pad) scu[pos] = __float2uint_rn(sv[r] * fx);
     }
     consumer_sync();
 
@@ -559,10 +631,15 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       wait_full();
       const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
       uint32_t dv[VSTEPS][VWPL], wv[VSTEPS];
+      const uint4 *wp = reinterpret_cast<const uint4 *>(scu + (t - t0) + warp * TPWV + tq * VSTEPS);
+#pragma unroll
+      for (int s4 = 0; s4 < VSTEPS / 4; ++s4) {
+        const uint4 w4 = wp[s4];
+        wv[4 * s4] = w4.x; wv[4 * s4 + 1] = w4.y; wv[4 * s4 + 2] = w4.z; wv[4 * s4 + 3] = w4.w;
+      }
 #pragma unroll
       for (int s = 0; s < VSTEPS; ++s) {
-        const int tok = warp * (TVN / CS_WARPS) + 4 * s + tq;
-        wv[s] = scu[t - t0 + tok];
+        const int tok = warp * TPWV + 4 * s + tq;
 #pragma unroll
         for (int m = 0; m < VWPL; ++m) dv[s][m] = stw[tok * VW + vword[m]];
       }
@@ -586,7 +663,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // ---- buckets -> rotated-domain accumulator -------------------------------------------
     // acc[j] = sum over byte values of bucket[byte][column(j)] * centroid[digit_j(byte)].
     // A thread owns one byte column and a slice of the 256 byte values, reads each
-    // bucket once and feeds the VE coordinates packed in that byte.
+    // bucket once, clears it for the next item and feeds the VE coordinates packed
+    // in that byte.
     {
       constexpr int NPARTS = CS_CONSUMERS / VC, BPP = 256 / NPARTS;
       const int col = tid % VC, part = tid / VC; // a warp shares `part`, so centroid reads broadcast
@@ -596,41 +674,39 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll 8
       for (int i = 0; i < BPP; ++i) {
         const int b = part * BPP + i;
-        uint32_t bi = COMPACT ? bucket[b * 32 + col] : bucket[b * 64 + col];
-        if (VC == 32 && !COMPACT) bi += bucket[b * 64 + 32 + col];
+        uint32_t bi;
+        if (COMPACT) {
+          bi = bucket[b * 32 + col];
+          bucket[b * 32 + col] = 0u;
+        } else {
+          bi = bucket[b * 64 + col];
+          bucket[b * 64 + col] = 0u;
+          if (VC == 32) {
+            bi += bucket[b * 64 + 32 + col];
+            bucket[b * 64 + 32 + col] = 0u;
+          }
+        }
         const float bv = (float)bi;
 #pragma unroll
         for (int e = 0; e < VE; ++e) av[e] += bv * s_cb[(b >> (8 - VB * (e + 1))) & ((1 << VB) - 1)];
       }
-      consumer_sync(); // all bucket reads done before sc[] is reused as fold space
+      // sc[] is free (the V stream has finished with the weights): use it as fold space
 #pragma unroll
       for (int e = 0; e < VE; ++e) sc[part * P + col * VE + e] = av[e] * inv_fx;
       consumer_sync();
-      if (tid < P) {
+      if (tid < P) { // hand the finished item to the helper warp and move on
         float t = 0.f;
 #pragma unroll
         for (int g = 0; g < NPARTS; ++g) t += sc[g * P + tid];
-        qr[tid] = t; // qr is free now
-      }
-      consumer_sync();
-    }
-    if (a.n_splits > 1 || a.force_partial) {
-      float *pp = a.partial + ((size_t)split * items_base + hq) * (size_t)(2 + P);
-      if (tid == 0) { pp[0] = mx; pp[1] = ls; }
-      if (tid < P) pp[2 + tid] = qr[tid];
-    } else if (warp == 0) { // normalise, inverse transform (core/fwht.cpp:106-134), write
-      float v[EPL];
-      const float invl = 1.f / ls;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) v[e] = qr[EPL * lane + e] * invl;
-      warp_butterflies<EPL>(v, lane);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        const int j = EPL * lane + e;
-        if (j < dim) a.out[(size_t)hq * dim + j] = v[e] * isp * (((sg_cur >> (j & 31)) & 1u) ? -1.f : 1.f);
+        const int ab = idx & 1;
+        guarded_wait(&aempty[ab], (((uint32_t)idx >> 1) & 1u) ^ 1u);
+        float *dst = accb + ab * ACC_PITCH;
+        dst[tid] = t;
+        if (tid == 0) { dst[P] = mx; dst[P + 1] = ls; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&afull[ab]);
       }
     }
-    consumer_sync();
     AQ_MARK(4)
   }
 #ifdef AQ_PROBE

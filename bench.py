@@ -53,9 +53,10 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS, help="sequences per GPU (default: the BASELINE config)")
     ap.add_argument("--context", type=int, default=CONTEXT)
-    ap.add_argument("--mode", default="decode", choices=["decode", "append", "latency"],
+    ap.add_argument("--mode", default="decode", choices=["decode", "append", "latency", "longctx"],
                     help="append: only the bulk-append kernel benchmark; latency: per-token decode latency of the "
-                         "small per-layer configurations (BASELINE configs[0..2])")
+                         "small per-layer configurations (BASELINE configs[0..2]); longctx: one 131072-token "
+                         "sequence with its KV range split over the ranks (BASELINE configs[4])")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-append-bench", action="store_true")
     ap.add_argument("--cpu-sample-heads", type=int, default=0)
@@ -292,6 +293,88 @@ def latency_bench(torch):
     return out
 
 
+def longctx_bench(torch, dist, world, rank, steps, warmup, peak):
+    """BASELINE configs[4]: ONE sequence, 1 layer, 32 KV heads, dim 128, context
+    131072, K2/V2 and K4/V4, K/V Student-t(nu=3), dense V.  Token t lives on rank
+    t mod G (local ring of 131072/G tokens).  One step = one decode query per
+    head: every rank runs the split-KV kernel over its shard, the (max, sum,
+    acc[128]) partials -- 16.6 KB per rank -- are all-gathered with NCCL and
+    merged, one inverse transform finishes.  Total work is fixed (strong
+    scaling).  L2 is flushed before every timed step, because at G >= 4 a
+    rank's shard (<= 71 MB) would otherwise stay in the 126 MB L2."""
+    import adaptq_b200
+    H, D, N = 32, 128, 131072
+    local_n = N // world
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    out = {}
+    for kb, vb in ((2, 2), (4, 4)):
+        ctx = adaptq_b200.MHAContext(H, D, kb, vb, local_n, seed=42, v_mass=0.0, hybrid_thresh=0)
+        g = torch.Generator(device="cuda").manual_seed(500 + rank)
+        done = 0
+        while done < local_n:
+            t = min(4096, local_n - done)
+            kv = []
+            for _ in range(2):
+                z = torch.randn((t, H, D), device="cuda", generator=g)
+                chi = torch.randn((t, H, D, 3), device="cuda", generator=g).pow(2).mean(-1)
+                kv.append(z / torch.sqrt(chi))  # Student-t, nu = 3
+            ctx.append_all(kv[0], kv[1], done)
+            done += t
+        gq = torch.Generator(device="cuda").manual_seed(77)  # the same query on every rank
+        q = torch.randn((H, D), device="cuda", generator=gq)
+        o = torch.empty((H, 1, D), device="cuda")
+        part = torch.empty((H, 1, 2 + D), device="cuda")
+        parts = torch.empty((world, H, 1, 2 + D), device="cuda")
+
+        def step_sharded():
+            ctx.compute_partial(q, out=part)
+            if dist is not None:
+                dist.all_gather_into_tensor(parts, part)
+                ctx.merge_partials(parts, nq=1, out=o)
+            else:
+                ctx.merge_partials(part.unsqueeze(0), nq=1, out=o)
+
+        def step_local():
+            ctx.compute_partial(q, out=part)
+
+        def step_single():
+            ctx.compute_all(q, out=o[:, 0])
+
+        def timed(fn):
+            for _ in range(max(3, warmup)):
+                fn()
+            tot = 0.0
+            for _ in range(steps):
+                flush.fill_(1)
+                torch.cuda.synchronize()
+                if dist is not None:
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                tot += a.elapsed_time(b)
+            t = torch.tensor([tot / steps], device="cuda")
+            if dist is not None:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item()) * 1e3  # us
+
+        alg = H * (N * (D * kb // 8 + D * vb // 8 + 8) + 8 * D)
+        us_total = timed(step_sharded)
+        us_local = timed(step_local)
+        res = {"us_per_step": us_total, "us_local_kernels": us_local, "us_gather_and_merge": us_total - us_local,
+               "effective_kv_gbs_all_ranks": alg / us_total / 1e3, "local_kernel_gbs_per_gpu": alg / world / us_local / 1e3,
+               "local_kernel_frac_of_peak": alg / world / us_local / 1e3 / peak,
+               "algorithmic_bytes": alg, "tokens_per_rank": local_n}
+        if world == 1:
+            res["us_per_step_compute_all"] = timed(step_single)
+        out[f"k{kb}v{vb}"] = res
+        ctx.close()
+    return out
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -314,6 +397,21 @@ def run_ours(args):
     if args.mode == "latency":
         if rank == 0:
             print(json.dumps({"metric": "decode_latency_us_per_token", "latency": latency_bench(torch)}))
+        return
+
+    if args.mode == "longctx":
+        res = longctx_bench(torch, dist, world, rank, args.steps, args.warmup, peak)
+        if rank == 0:
+            print(json.dumps({"metric": "long_context_decode_us_per_step", "unit": "us", "n_gpus": world,
+                              "steps": args.steps, "higher_is_better": False, "scaling": "strong", "dtype": "f32",
+                              "data": "synthetic",
+                              "config": {"workload": "one sequence, 32 KV heads, dim 128, context 131072, KV range split "
+                                                     "by token over the ranks, NCCL all-gather of split-KV partials "
+                                                     "(BASELINE configs[4])", "l2": "L2 flushed before every timed step"},
+                              "results": res}))
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return
 
     heads = args.seqs * LAYERS * KV_HEADS

@@ -176,6 +176,26 @@ __device__ __forceinline__ float group_transpose_sum(float (&v)[STEPS], int wl) 
   return v[0];
 }
 
+// The same over the 4 lanes of a token group: 4 steps -> lane wl owns step wl;
+// 2 steps -> lanes 2*s and 2*s+1 both end with step s.
+template <int STEPS>
+__device__ __forceinline__ float quad_transpose_sum(float (&v)[STEPS], int wl) {
+  static_assert(STEPS == 2 || STEPS == 4, "2 or 4 steps");
+  const bool up2 = (wl & 2) != 0, up1 = (wl & 1) != 0;
+  if constexpr (STEPS == 4) {
+    const float k0 = up2 ? v[2] : v[0], s0 = up2 ? v[0] : v[2];
+    const float k1 = up2 ? v[3] : v[1], s1 = up2 ? v[1] : v[3];
+    const float x0 = k0 + __shfl_xor_sync(0xffffffffu, s0, 2);
+    const float x1 = k1 + __shfl_xor_sync(0xffffffffu, s1, 2);
+    const float k = up1 ? x1 : x0, s = up1 ? x0 : x1;
+    return k + __shfl_xor_sync(0xffffffffu, s, 1);
+  } else {
+    const float k = up2 ? v[1] : v[0], s = up2 ? v[0] : v[1];
+    const float x = k + __shfl_xor_sync(0xffffffffu, s, 2);
+    return x + __shfl_xor_sync(0xffffffffu, x, 1);
+  }
+}
+
 // KB/VB: bits; KW/VW: 32-bit words per packed row (8 or 16).
 template <int KB, int KW, int VB, int VW>
 __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const StreamLaunch a) {
@@ -183,8 +203,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   static_assert(P == VW * 32 / VB, "K and V rows must describe the same padded dimension");
   constexpr int KROW = KW * 4, VROW = VW * 4;
   constexpr int TKN = CS_STAGE_BYTES / KROW, TVN = CS_STAGE_BYTES / VROW; // tokens per stage
-  constexpr int KSTEPS = TKN / CS_WARPS / 4, VSTEPS = TVN / CS_WARPS / 4;   // 4 tokens per warp step
-  constexpr int KWPL = KW / 8, VWPL = VW / 8;                               // words per lane
+  // Lanes that share a token in the K stream: 4 with 32-byte rows, 8 with 64-byte rows
+  // (measured: fewer shuffles pay with the short rows, not with the long ones).
+  constexpr int KLPT = KW == 16 ? 8 : 4;
+  constexpr int KTPS = 32 / KLPT;                                           // tokens per warp step (K)
+  constexpr int KSTEPS = TKN / CS_WARPS / KTPS, VSTEPS = TVN / CS_WARPS / 4; // V: 4 tokens per warp step
+  constexpr int KWPL = KW / KLPT, VWPL = VW / 8;                            // words per lane
   constexpr int KC = KW * 4, VC = VW * 4;                                   // byte columns
   constexpr int KE = 8 / KB, VE = 8 / VB;                                   // coordinates per byte
   constexpr bool COMPACT = AQ_COMPACT_BUCKETS && VC == 32;
@@ -296,9 +320,13 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       const uint8_t *kb = c.k_slab + (size_t)h * c.k_stride;
       const uint8_t *vb = c.v_slab + (size_t)h * c.v_stride;
       const float *ksb = c.k_scale + (size_t)h * c.s_stride;
-      for (int pass = 0; pass < 2; ++pass) {
-        const int rowb = pass ? VROW : KROW, tn = pass ? TVN : TKN;
-        const uint8_t *src = pass ? vb : kb;
+      const uint8_t *vsb = reinterpret_cast<const uint8_t *>(c.v_scale + (size_t)h * c.s_stride);
+      // three passes over the span: K rows (with their scales), the V scales as
+      // plain 16 KB tiles for the softmax phase, then the V rows
+      for (int pass = 0; pass < 3; ++pass) {
+        const int rowb = pass == 0 ? KROW : pass == 1 ? 4 : VROW;
+        const int tn = pass == 0 ? TKN : pass == 1 ? CS_STAGE_BYTES / 4 : TVN;
+        const uint8_t *src = pass == 0 ? kb : pass == 1 ? vsb : vb;
         for (int t = t0; t < t1; t += tn) {
           if (*reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(&empty[stage], phase ^ 1u)) {
             *reinterpret_cast<volatile int *>(s_fail) = 1;
@@ -397,10 +425,19 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   // Per-lane constants.  The lane reads word kword[m] of its token's row and
   // visits that word's four bytes in the rotated order (k + tq) & 3, which puts
   // the 32 lanes of a warp on 32 different banks of the table / bucket arrays.
+  // K stream with four lanes per token (lane = 4*kg + kwl, kg = token within the
+  // step): the lane takes words kwl + 4*j of the row, in an order rotated by the
+  // token, so that the 32 data-word reads of a step and the 32 table reads of a
+  // byte position each fall on 32 different banks.
+  const int kg = KLPT == 4 ? lane >> 2 : tq, kwl = KLPT == 4 ? lane & 3 : wl;
   int kword[KWPL], vword[VWPL];
-  uint32_t ksel[4], kconst[KWPL][4], vconst[VWPL][4];
+  uint32_t ksel[4], kselk[4], kconst[KWPL][4], vconst[VWPL][4];
 #pragma unroll
-  for (int m = 0; m < KWPL; ++m) kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+  for (int m = 0; m < KWPL; ++m) {
+    if (KLPT == 4) kword[m] = KW == 16 ? kwl + 4 * ((m + (kg >> 1)) & 3) : kwl + 4 * ((m + (kg >> 2)) & 1);
+    else kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+  }
+  const int krot = KLPT == 4 ? (KW == 16 ? (kg & 1) + 2 * (kg >> 2) : (kg & 3)) : tq;
 #pragma unroll
   for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
   // With 32 byte columns (2-bit V at dim 128, 4-bit at dim 64) the 64-column rows
@@ -410,8 +447,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   for (int k = 0; k < 4; ++k) {
     const int kk = (k + tq) & 3;
     ksel[k] = 0x7604u | ((uint32_t)kk << 4); // result = {const.b0, data.byte[kk], const.b2, const.b3}
+    const int kkk = (k + krot) & 3;
+    kselk[k] = 0x7604u | ((uint32_t)kkk << 4);
 #pragma unroll
-    for (int m = 0; m < KWPL; ++m) kconst[m][k] = table_addr | (uint32_t)((4 * kword[m] + kk) << 2);
+    for (int m = 0; m < KWPL; ++m) kconst[m][k] = table_addr | (uint32_t)((4 * kword[m] + kkk) << 2);
 #pragma unroll
     // bucket rows are 64 columns (256 bytes), so the packed byte lands in address
     // bits 8..15 with one byte-permute
@@ -442,7 +481,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     next_ready = mbar_test(&full[ns], np);
   };
   auto wait_full = [&]() {
-#ifdef AQ_PROBE
+#if defined(AQ_PROBE) && AQ_PROBE > 1
     const long long w0__ = clock64();
 #endif
     // The stage was already tested (peek_next) while the previous tile was being
@@ -451,7 +490,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       *reinterpret_cast<volatile int *>(s_fail) = 1;
       atomicExch(a.status, 1);
     }
-#ifdef AQ_PROBE
+#if defined(AQ_PROBE) && AQ_PROBE > 1
     if (tid == 0) {
       const unsigned long long dt__ = (unsigned long long)(clock64() - w0__);
       probe_acc[probe_phase] += dt__;
@@ -472,15 +511,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   int prev_hq = -1, quse = 0;
   for (int item = item_begin, idx = 0; item < item_end; ++item, ++idx) {
     const int split = item % a.n_splits, hq = item / a.n_splits;
-    const int hl = hq / a.nq;
-    const int h = a.head0 + hl;
     const int t0 = min(a.n, split * a.span), t1 = min(a.n, t0 + a.span);
     const int len = t1 - t0;
-    { // pull this span's V scale lines into L2; they are read after the K stream
-      const float *sp = c.v_scale + (size_t)h * c.s_stride + t0;
-      const int off = tid * 32; // floats; 128-byte lines
-      if (off < len) asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + off));
-    }
+
     if (hq == prev_hq) {
       // same (head, query) as the previous item: the table stands.  The barrier keeps
       // this item's score writes behind the last fold reads of the previous item.
@@ -536,9 +569,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // After the group reduction one lane per token owns its dot product; that lane
     // also reads the token's K scale (it arrived with the stage) and keeps a running
     // maximum, so no separate scaling pass is needed.
-    const float *vsc = c.v_scale + (size_t)h * c.s_stride + t0;
-    const int own_tok = warp * (TKN / CS_WARPS) + 4 * (KSTEPS == 8 ? wl : (wl >> 1)) + tq;
-    const bool owner = KSTEPS == 8 || (wl & 1) == 0;
+    // which token of the warp's slice this lane owns after the group reduction
+    const int own_step = KLPT == 4 ? (KSTEPS == 4 ? kwl : (kwl >> 1)) : (KSTEPS == 8 ? wl : (wl >> 1));
+    const bool owner = KLPT == 4 ? (KSTEPS == 4 || (kwl & 1) == 0) : (KSTEPS == 8 || (wl & 1) == 0);
+    const int own_tok = warp * (TKN / CS_WARPS) + KTPS * own_step + kg;
     float lane_max = -INFINITY;
     for (int t = t0; t < t1; t += TKN) {
       wait_full();
@@ -548,7 +582,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       uint32_t dk[KSTEPS][KWPL];
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
-        const int tok = warp * (TKN / CS_WARPS) + 4 * s + tq; // token within the stage
+        const int tok = warp * (TKN / CS_WARPS) + KTPS * s + kg; // token within the stage
 #pragma unroll
         for (int m = 0; m < KWPL; ++m) dk[s][m] = stw[tok * KW + kword[m]];
       }
@@ -560,14 +594,16 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
         for (int m = 0; m < KWPL; ++m) {
           const uint32_t d = dk[s][m];
-          a0 += lds_f32(__byte_perm(d, kconst[m][0], ksel[0]));
-          a1 += lds_f32(__byte_perm(d, kconst[m][1], ksel[1]));
-          a0 += lds_f32(__byte_perm(d, kconst[m][2], ksel[2]));
-          a1 += lds_f32(__byte_perm(d, kconst[m][3], ksel[3]));
+          a0 += lds_f32(__byte_perm(d, kconst[m][0], kselk[0]));
+          a1 += lds_f32(__byte_perm(d, kconst[m][1], kselk[1]));
+          a0 += lds_f32(__byte_perm(d, kconst[m][2], kselk[2]));
+          a1 += lds_f32(__byte_perm(d, kconst[m][3], kselk[3]));
         }
         pv[s] = a0 + a1;
       }
-      const float total = group_transpose_sum<KSTEPS>(pv, wl);
+      float total;
+      if constexpr (KLPT == 4) total = quad_transpose_sum<KSTEPS>(pv, kwl);
+      else total = group_transpose_sum<KSTEPS>(pv, wl);
       if (own_valid) {
         const float logit = total * attn_s * ksv;
         sc[t - t0 + own_tok] = logit;
@@ -576,16 +612,28 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       release();
     }
     // ---- exact two-pass softmax over the span ------------------------------------------
-    // Each thread owns tokens tid, tid+512, ...; their scales are fetched in one
-    // batch (the lines were pulled into L2 at the start of the item; the loads
-    // are issued before the barrier so their latency overlaps the wait) and every
-    // intermediate stays in registers.
+    // Each thread owns tokens tid, tid+512, ...; their V scales come through the
+    // ring (4096 per stage) and every intermediate stays in registers.
     constexpr int NPT = CS_SPAN_MAX / CS_CONSUMERS;
+    constexpr int SCT = CS_STAGE_BYTES / 4;       // scales per stage
+    constexpr int RPS = SCT / CS_CONSUMERS;       // ... = this many of a thread's tokens
     float sv[NPT], vv[NPT];
 #pragma unroll
-    for (int r = 0; r < NPT; ++r) {
-      const int i = tid + r * CS_CONSUMERS;
-      vv[r] = i < len ? __ldg(vsc + i) : 0.f;
+    for (int cchunk = 0; cchunk < NPT / RPS; ++cchunk) {
+      if (cchunk * SCT < len) {
+        wait_full();
+        const float *vs = reinterpret_cast<const float *>(stage_ptr(stage));
+        peek_next();
+#pragma unroll
+        for (int rr = 0; rr < RPS; ++rr) {
+          const int r = cchunk * RPS + rr;
+          vv[r] = tid + r * CS_CONSUMERS < len ? vs[tid + rr * CS_CONSUMERS] : 0.f;
+        }
+        release();
+      } else {
+#pragma unroll
+        for (int rr = 0; rr < RPS; ++rr) vv[cchunk * RPS + rr] = 0.f;
+      }
     }
     AQ_MARK(1)
     const float mx = consumer_max(lane_max, red_max); // its barrier also publishes sc[]
@@ -667,11 +715,25 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // in that byte.
     {
       constexpr int NPARTS = CS_CONSUMERS / VC, BPP = 256 / NPARTS;
-      const int col = tid % VC, part = tid / VC; // a warp shares `part`, so centroid reads broadcast
-      float av[VE];
+      constexpr int LOGB = BPP == 16 ? 4 : 5; // byte value = (part << LOGB) | i
+      static_assert(BPP == 16 || BPP == 32, "16 or 32 byte values per thread");
+      const int col = tid % VC, part = tid / VC; // a warp shares `part`
+      const float *vcb = c_cb[VB - 2];
+      // The digit of coordinate e is bits [sh, sh+VB) of the byte value, sh = 8 - VB*(e+1).
+      // With the loop over i unrolled it is a compile-time constant where those bits lie
+      // inside i, fixed per thread where they lie inside `part` (then the buckets are
+      // summed first and multiplied once), and one of two per-thread values in between.
+      float av[VE], psum[VE], cmix[VE][2];
 #pragma unroll
-      for (int e = 0; e < VE; ++e) av[e] = 0.f;
-#pragma unroll 8
+      for (int e = 0; e < VE; ++e) {
+        constexpr int MASK = (1 << VB) - 1;
+        const int sh = 8 - VB * (e + 1);
+        av[e] = 0.f;
+        psum[e] = 0.f;
+        cmix[e][0] = vcb[((part << LOGB) >> sh) & MASK];
+        cmix[e][1] = vcb[(((part << LOGB) | (1 << (LOGB - 1))) >> sh) & MASK];
+      }
+#pragma unroll
       for (int i = 0; i < BPP; ++i) {
         const int b = part * BPP + i;
         uint32_t bi;
@@ -688,7 +750,18 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         }
         const float bv = (float)bi;
 #pragma unroll
-        for (int e = 0; e < VE; ++e) av[e] += bv * s_cb[(b >> (8 - VB * (e + 1))) & ((1 << VB) - 1)];
+        for (int e = 0; e < VE; ++e) {
+          constexpr int MASK = (1 << VB) - 1;
+          const int sh = 8 - VB * (e + 1);
+          if (sh >= LOGB) psum[e] += bv;                                        // digit set by `part`
+          else if (sh + VB <= LOGB) av[e] += bv * vcb[(i >> sh) & MASK];         // digit set by i
+          else av[e] += bv * cmix[e][(i >> (LOGB - 1)) & 1];                     // top bit of i, rest from `part`
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const int sh = 8 - VB * (e + 1);
+        if (sh >= LOGB) av[e] = psum[e] * cmix[e][0];
       }
       // sc[] is free (the V stream has finished with the weights): use it as fold space
 #pragma unroll

@@ -37,6 +37,18 @@ class Engine:
         self._ctx.append_all(k, v, self.pos)
         self.pos += int(k.shape[0])
 
+    def step(self, k, v, q):
+        """append(k, v) followed by compute(q) as one library call (what upstream's
+        AdaptQAttention.forward does per token, adaptq/torch_adapter.py:100-108)."""
+        want = (self.heads, self.dim)
+        if tuple(k.shape) != want or tuple(v.shape) != want:
+            raise ValueError(f"k and v must be shape ({self.heads}, {self.dim})")
+        if tuple(q.shape) != want:
+            raise ValueError(f"q must be shape ({self.heads}, {self.dim})")
+        out = self._ctx.decode_step(k, v, q, pos=self.pos)
+        self.pos += 1
+        return out
+
     def compute(self, q):
         """q: (heads, dim) -> float32 (heads, dim), numpy in / numpy out, tensor in / tensor out."""
         if tuple(q.shape) != (self.heads, self.dim):

@@ -81,6 +81,9 @@ struct Group {
   int *d_status = nullptr;
   size_t device_bytes = 0;
   std::mutex mu;
+  // decode-step pipeline (host buffers): copy streams and per-chunk events, made on first use
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  std::vector<cudaEvent_t> ev;
 
   RingState state(int h) const { return uniform ? u : per_head[h]; }
   void split_state() {
@@ -130,6 +133,9 @@ void free_group(Group *g) {
   cudaFree((void *)g->c.signs); cudaFree(g->c.mirror);
   cudaFree(g->d_stage); cudaFree(g->d_scratch); cudaFree(g->d_status);
   if (g->h_stage) cudaFreeHost(g->h_stage);
+  if (g->copy_in) cudaStreamDestroy(g->copy_in);
+  if (g->copy_out) cudaStreamDestroy(g->copy_out);
+  for (cudaEvent_t e : g->ev) cudaEventDestroy(e);
   g->magic = 0;
   delete g;
 }
@@ -515,11 +521,12 @@ bool stream_supported(const CacheView &c) {
   return false;
 }
 
-// Pick the number of KV spans per (head, query): spans are multiples of 512
-// tokens (the largest stage tile), at most CS_SPAN_MAX, not needlessly short,
+// Pick the number of KV spans per (head, query): spans are multiples of 64
+// tokens (16-byte aligned rows and scales; a span's last stage tile may be
+// partial) of nearly equal length, at most CS_SPAN_MAX, not needlessly short,
 // and the item count should fill whole waves of persistent blocks.
 void plan_spans(int n, int items_base, int sms, int &n_splits, int &span) {
-  const int G = 512;
+  const int G = 64;
   const int n_pad = (int)round_up((size_t)n, G);
   const int min_splits = (n + CS_SPAN_MAX - 1) / CS_SPAN_MAX;
   double best = -1.0;
@@ -911,6 +918,77 @@ int adaptq_mha_compute_all(adaptq_mha_t h, const float *queries, int queries_per
     return -1;
   clear_error();
   return compute_all_impl(g, queries, queries_per_head, outs, false, "adaptq_mha_compute_all");
+}
+
+// One decode step over all heads: append one token per head, then one query per
+// head.  With pinned host buffers the heads are cut into chunks and the chunks
+// are pipelined over three streams -- upload of chunk i+1, kernels of chunk i and
+// download of chunk i-1 overlap -- so the PCIe time hides behind the kernels.
+#define STEP_TRY(expr)                                                                         \
+  do {                                                                                         \
+    cudaError_t e__ = (expr);                                                                  \
+    if (e__ != cudaSuccess) {                                                                  \
+      set_error("adaptq_mha_decode_step: CUDA error: %s", cudaGetErrorString(e__));            \
+      return -1;                                                                               \
+    }                                                                                          \
+  } while (0)
+int adaptq_mha_decode_step(adaptq_mha_t h, const float *keys, const float *vals, const float *queries, float *outs,
+                           int token_pos) {
+  MHA_PROLOGUE("adaptq_mha_decode_step", -1)
+  if (!require_pointer(keys, "adaptq_mha_decode_step", "keys") || !require_pointer(vals, "adaptq_mha_decode_step", "vals") ||
+      !require_pointer(queries, "adaptq_mha_decode_step", "queries") || !require_pointer(outs, "adaptq_mha_decode_step", "outs"))
+    return -1;
+  clear_error();
+  const CacheView &c = g->c;
+  constexpr int CHUNKS = 8;
+  const bool pinned = ptr_kind(keys) == PK_HOST_PINNED && ptr_kind(vals) == PK_HOST_PINNED &&
+                      ptr_kind(queries) == PK_HOST_PINNED && ptr_kind(outs) == PK_HOST_PINNED;
+  std::unique_lock<std::mutex> lk(g->mu);
+  const bool pipeline = pinned && g->uniform && c.v_mass <= 0.f && c.n_heads >= 4096;
+  if (!pipeline) {
+    lk.unlock();
+    if (adaptq_mha_append_batch(h, keys, vals, 1, token_pos) != 0) return -1;
+    return adaptq_mha_compute_all(h, queries, 1, outs);
+  }
+  DeviceGuard dg(g->device);
+  const size_t row = (size_t)c.dim, all = (size_t)c.n_heads * row * 4, slot = round_up(all, 256);
+  if (!ensure_stage(g, 4 * slot, 0)) return -1;
+  if (!g->copy_in) {
+    STEP_TRY(cudaStreamCreateWithFlags(&g->copy_in, cudaStreamNonBlocking));
+    STEP_TRY(cudaStreamCreateWithFlags(&g->copy_out, cudaStreamNonBlocking));
+  }
+  while (g->ev.size() < 2 * CHUNKS + 1) {
+    cudaEvent_t e;
+    STEP_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    g->ev.push_back(e);
+  }
+  char *st = static_cast<char *>(g->d_stage);
+  float *dk = reinterpret_cast<float *>(st), *dv = reinterpret_cast<float *>(st + slot),
+        *dq = reinterpret_cast<float *>(st + 2 * slot), *dout = reinterpret_cast<float *>(st + 3 * slot);
+  // the staging buffer may still be in use by earlier work of this handle
+  STEP_TRY(cudaEventRecord(g->ev[2 * CHUNKS], g->stream));
+  STEP_TRY(cudaStreamWaitEvent(g->copy_in, g->ev[2 * CHUNKS], 0));
+  const RingState before = g->u, after = advance(c, before, 1);
+  const int per = (c.n_heads + CHUNKS - 1) / CHUNKS;
+  for (int ch = 0; ch < CHUNKS; ++ch) {
+    const int h0 = ch * per, hc = std::min(per, c.n_heads - h0);
+    if (hc <= 0) break;
+    const size_t off = (size_t)h0 * row, bytes = (size_t)hc * row * 4;
+    STEP_TRY(cudaMemcpyAsync(dk + off, keys + off, bytes, cudaMemcpyHostToDevice, g->copy_in));
+    STEP_TRY(cudaMemcpyAsync(dv + off, vals + off, bytes, cudaMemcpyHostToDevice, g->copy_in));
+    STEP_TRY(cudaMemcpyAsync(dq + off, queries + off, bytes, cudaMemcpyHostToDevice, g->copy_in));
+    STEP_TRY(cudaEventRecord(g->ev[ch], g->copy_in));
+    STEP_TRY(cudaStreamWaitEvent(g->stream, g->ev[ch], 0));
+    if (!append_device(g, dk + off, dv + off, h0, hc, 1, (size_t)c.n_heads * row, before)) return -1;
+    if (!compute_device(g, dq + off, dout + off, h0, hc, 1, after, false)) return -1;
+    STEP_TRY(cudaEventRecord(g->ev[CHUNKS + ch], g->stream));
+    STEP_TRY(cudaStreamWaitEvent(g->copy_out, g->ev[CHUNKS + ch], 0));
+    STEP_TRY(cudaMemcpyAsync(outs + off, dout + off, bytes, cudaMemcpyDeviceToHost, g->copy_out));
+  }
+  g->u = after;
+  STEP_TRY(cudaStreamSynchronize(g->copy_out));
+  STEP_TRY(cudaStreamSynchronize(g->stream));
+  return after.size;
 }
 
 int adaptq_mha_partial_floats(adaptq_mha_t h) {

@@ -229,32 +229,80 @@ __global__ void __launch_bounds__(CG_THREADS) merge_partials_kernel(
   const int h = head0 + item / nq;
   const int tid = threadIdx.x;
   const float *base = parts + (size_t)item * (2 + P);
-  float M = -INFINITY;
-  for (int p = 0; p < n_parts; ++p) {
+  // All loads of a step are independent of each other, so their latencies
+  // overlap: the (max, sum) pairs are read one part per thread, the
+  // accumulators with the parts dealt round-robin to thread groups.
+  __shared__ float s_w[1024];        // weight exp(m_p - M) of the first 1024 parts
+  __shared__ float s_red[CG_WARPS];
+  __shared__ float s_grp[CG_THREADS];
+  const int lane = tid & 31, warp = tid >> 5;
+  float m_loc = -INFINITY;
+  for (int p = tid; p < n_parts; p += CG_THREADS) {
     const float *pp = base + (size_t)p * part_stride;
-    if (pp[1] > 0.f) M = fmaxf(M, pp[0]);
+    if (pp[1] > 0.f) m_loc = fmaxf(m_loc, pp[0]);
   }
+  m_loc = warp_max(m_loc);
+  if (lane == 0) s_red[warp] = m_loc;
+  __syncthreads();
+  float M = s_red[0];
+  for (int w = 1; w < CG_WARPS; ++w) M = fmaxf(M, s_red[w]);
+  __syncthreads();
+  float l_loc = 0.f;
+  for (int p = tid; p < n_parts; p += CG_THREADS) {
+    const float *pp = base + (size_t)p * part_stride;
+    const float l = pp[1];
+    const float w = l > 0.f ? expf(pp[0] - M) : 0.f;
+    if (p < 1024) s_w[p] = w;
+    l_loc += l > 0.f ? l * w : 0.f;
+  }
+  l_loc = warp_sum(l_loc);
+  if (lane == 0) s_red[warp] = l_loc;
+  __syncthreads(); // also publishes s_w
   float L = 0.f;
-  for (int p = 0; p < n_parts; ++p) {
-    const float *pp = base + (size_t)p * part_stride;
-    if (pp[1] > 0.f) L += pp[1] * expf(pp[0] - M);
-  }
+  for (int w = 0; w < CG_WARPS; ++w) L += s_red[w];
   const float invL = to_partial ? 1.f : 1.f / L;
-  for (int j = tid; j < P; j += CG_THREADS) {
+  auto weight = [&](int p) -> float {
+    if (p < 1024) return s_w[p];
+    const float *pp = base + (size_t)p * part_stride;
+    return pp[1] > 0.f ? expf(pp[0] - M) : 0.f;
+  };
+  if (P <= CG_THREADS) {
+    const int groups = CG_THREADS / P, g = tid / P, j = tid % P;
     float s = 0.f;
-    for (int p = 0; p < n_parts; ++p) {
-      const float *pp = base + (size_t)p * part_stride;
-      if (pp[1] > 0.f) s += pp[2 + j] * expf(pp[0] - M);
+    if (g < groups) {
+#pragma unroll 8
+      for (int p = g; p < n_parts; p += groups) {
+        const float w = weight(p);
+        const float v = w > 0.f ? base[(size_t)p * part_stride + 2 + j] : 0.f;
+        s += v * w;
+      }
     }
-    vec[j] = s * invL;
+    s_grp[tid] = s;
+    __syncthreads();
+    if (tid < P) {
+      float t = 0.f;
+      for (int gg = 0; gg < groups; ++gg) t += s_grp[gg * P + tid];
+      vec[tid] = t * invL;
+    }
+  } else {
+    for (int j = tid; j < P; j += CG_THREADS) {
+      float s = 0.f;
+#pragma unroll 8
+      for (int p = 0; p < n_parts; ++p) {
+        const float w = weight(p);
+        const float v = w > 0.f ? base[(size_t)p * part_stride + 2 + j] : 0.f;
+        s += v * w;
+      }
+      vec[j] = s * invL;
+    }
   }
+  __syncthreads();
   if (to_partial) { // one combined, still un-normalised partial per (head, query)
     float *po = out + (size_t)item * (2 + P);
     if (tid == 0) { po[0] = M; po[1] = L; }
     for (int j = tid; j < P; j += CG_THREADS) po[2 + j] = vec[j];
     return;
   }
-  __syncthreads();
   float *o = out + (size_t)item * dim;
   if (v_f32) {
     for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j];

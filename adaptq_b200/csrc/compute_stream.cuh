@@ -75,7 +75,7 @@ struct StreamLaunch {
   float *out;     // [heads_in_call][nq][dim]                 (n_splits == 1)
   float *partial; // [n_splits][heads_in_call*nq][2+P]        (n_splits  > 1)
   int head0, heads_in_call, nq;
-  int n, n_splits, span; // span: tokens per split, multiple of 512
+  int n, n_splits, span; // span: tokens per split, multiple of 64
   int force_partial;     // write the partial even when there is a single span
   int *status;
 #ifdef AQ_PROBE
@@ -469,6 +469,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   unsigned long long probe_mywait = 0;
   unsigned long long probe_hist[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   long long probe_last = clock64();
+  unsigned long long probe_gt0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(probe_gt0));
+  const long long probe_c0 = probe_last;
   int probe_phase = 5;
 #endif
   bool next_ready = false;
@@ -785,6 +788,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #ifdef AQ_PROBE
   if (tid == 0 && a.probe)
     for (int k = 0; k < 7; ++k) atomicAdd(a.probe + k, probe_acc[k]);
+  if (tid == 0 && blockIdx.x == 0 && a.probe) { // SM clock seen by block 0: cycles / nanoseconds
+    unsigned long long gt1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
+    a.probe[7] = gt1 - probe_gt0;
+    a.probe[30] = (unsigned long long)(clock64() - probe_c0);
+  }
   if (lane == 0 && a.probe) atomicAdd(a.probe + 8 + warp, probe_mywait);
   if (tid == 0 && a.probe)
     for (int k = 0; k < 8; ++k) atomicAdd(a.probe + 24 + k, probe_hist[k]);

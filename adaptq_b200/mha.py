@@ -142,6 +142,23 @@ class MHAContext:
             raise RuntimeError(_lib.last_error())
         return ok
 
+    def decode_step(self, keys, vals, queries, out=None, pos=0):
+        """One decode step for all heads: append keys/vals [n_heads, dim], then attend
+        with queries [n_heads, dim].  Same result as append_all + compute_all; with
+        page-locked host arrays the transfers overlap the kernels."""
+        kp, kk, _ = _as_arg(keys)
+        vp, vk, _ = _as_arg(vals)
+        qp, qk, _ = _as_arg(queries)
+        want = (self._n_heads, self._head_dim)
+        if tuple(kk.shape) != want or tuple(vk.shape) != want or tuple(qk.shape) != want:
+            raise ValueError(f"keys, vals and queries must be shape ({self._n_heads}, {self._head_dim})")
+        if out is None:
+            out = torch.empty_like(qk) if (torch is not None and isinstance(qk, torch.Tensor)) else np.empty_like(qk)
+        op, ok, _ = _as_arg(out)
+        if self._L.adaptq_mha_decode_step(self._h, kp, vp, qp, op, pos) < 0:
+            raise RuntimeError(_lib.last_error())
+        return ok
+
     def compute_partial(self, queries, out=None):
         """Un-normalised split-KV partials [n_heads, nq, 2+padded] for sequence sharding."""
         qp, qk, _ = _as_arg(queries)

@@ -42,8 +42,7 @@ class AdaptQAttention(nn.Module):
         k32 = k.detach()[0].to(torch.float32).contiguous()
         v32 = v.detach()[0].to(torch.float32).contiguous()
         q32 = q.detach()[0].to(torch.float32).contiguous()
-        self.engine.append(k32, v32)
-        out = self.engine.compute(q32)
+        out = self.engine.step(k32, v32, q32)
         return out.unsqueeze(0).to(device=q.device, dtype=q.dtype)
 
     def reset_cache(self) -> None:

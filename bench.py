@@ -17,7 +17,8 @@ decode attention for one query per head.  value = sequences * steps / time
 
 The line also carries:
   e2e          the same step driven from pinned HOST buffers through the C ABI
-               (H2D of K, V, q and D2H of the outputs inside the timed region)
+               (adaptq_mha_decode_step: H2D of K, V, q and D2H of the outputs
+               inside the timed region)
   roofline     streaming decode kernel: algorithmic KV bytes / measured kernel time
                against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
   append       bulk-append kernel throughput (vectors/s) and its roofline
@@ -434,9 +435,8 @@ def run_ours(args):
         ctx.append_all(d_k, d_v)
         ctx.compute_all(d_q, out=d_o)
 
-    def step_host():
-        ctx.append_all(h_k, h_v)
-        ctx.compute_all(h_q, out=h_o)
+    def step_host():  # one C-ABI call: uploads, kernels and the download are pipelined inside
+        ctx.decode_step(h_k, h_v, h_q, out=h_o)
 
     def barrier():
         torch.cuda.synchronize()

@@ -46,6 +46,21 @@ int adaptq_mha_append_batch(adaptq_mha_t mha, const float *keys,
 int adaptq_mha_compute_all(adaptq_mha_t mha, const float *queries,
                            int queries_per_head, float *outs);
 
+/* One decode step for every head: append one token per head, then attend
+ * with one query per head.  keys, vals, queries, outs: float [n_heads][dim].
+ * Equals adaptq_mha_append_batch(mha, keys, vals, 1, token_pos) followed by
+ * adaptq_mha_compute_all(mha, queries, 1, outs) -- what upstream's
+ * AdaptQAttention.forward does per token (adaptq/torch_adapter.py:100-108,
+ * Engine.append then Engine.compute).  When all four buffers are page-locked
+ * host memory (and the handle has at least 4096 heads moving in lockstep,
+ * dense V) the heads are processed in chunks whose uploads, kernels and
+ * downloads overlap on separate CUDA streams, so the host transfers hide
+ * behind the kernels; otherwise the two calls run one after the other.
+ * Returns the token count after the append, or -1. */
+int adaptq_mha_decode_step(adaptq_mha_t mha, const float *keys,
+                           const float *vals, const float *queries,
+                           float *outs, int token_pos);
+
 /* Sequence sharding.  When the tokens of ONE logical cache are spread over
  * several handles (for instance token t on GPU t mod G), each handle
  * produces un-normalised softmax partials in the rotated domain:

@@ -1,0 +1,81 @@
+"""adaptq_mha_decode_step: one call = append of one token per head + attention.
+
+It must give exactly what adaptq_mha_append_batch followed by
+adaptq_mha_compute_all gives (same kernels, same order per head), both on the
+plain path (few heads, pageable host memory) and on the pipelined path
+(>= 4096 heads, page-locked host buffers, chunks overlapped on three streams),
+and leave the cache in the same state.  The small case is also checked
+against the CPU oracle.
+"""
+import numpy as np
+import pytest
+
+from helpers import CpuHeads, assert_cache_equal, assert_close, make_kv
+
+pytestmark = pytest.mark.gpu
+
+
+def test_decode_step_small_against_oracle(gpu_lib, orc):
+    import adaptq_b200
+    heads, dim, cap = 6, 64, 48
+    rng = np.random.default_rng(3)
+    k, v = make_kv(rng, 60, heads, dim)
+    q = rng.standard_normal((60, heads, dim)).astype(np.float32)
+    ctx = adaptq_b200.MHAContext(heads, dim, 4, 2, cap, seed=9, v_mass=0.0, hybrid_thresh=0)
+    cpu = CpuHeads(orc, heads, dim, 4, 2, cap, 9)
+    for t in range(60):  # wraps the ring
+        out = ctx.decode_step(k[t], v[t], q[t], pos=t)
+        cpu.append_many(k[t:t + 1], v[t:t + 1])
+        if t % 7 == 0 or t == 59:
+            assert_close(out, cpu.compute(q[t]), f"decode_step t={t}")
+    for h in (0, heads - 1):
+        assert_cache_equal(ctx.export_head(h), cpu.heads[h], f"head {h}")
+    ctx.close()
+
+
+@pytest.mark.parametrize("bits", [(4, 2), (2, 4)])
+def test_decode_step_pipelined_equals_two_calls(gpu_lib, bits):
+    import torch
+    import adaptq_b200
+    heads, dim, cap = 4096 + 40, 128, 96  # not a multiple of the chunk count
+    kb, vb = bits
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = adaptq_b200.MHAContext(heads, dim, kb, vb, cap, seed=5, v_mass=0.0, hybrid_thresh=0)
+    b = adaptq_b200.MHAContext(heads, dim, kb, vb, cap, seed=5, v_mass=0.0, hybrid_thresh=0)
+    pre_k = torch.randn((cap - 2, heads, dim), device="cuda", generator=g)
+    pre_v = torch.randn((cap - 2, heads, dim), device="cuda", generator=g)
+    a.append_all(pre_k, pre_v)
+    b.append_all(pre_k, pre_v)
+    launches0 = gpu_lib.adaptq_kernel_launches()
+    for step in range(4):  # the last two steps evict
+        k = torch.randn((heads, dim), device="cuda", generator=g)
+        v = torch.randn((heads, dim), device="cuda", generator=g)
+        q = torch.randn((heads, dim), device="cuda", generator=g)
+        hk, hv, hq = (t.cpu().pin_memory() for t in (k, v, q))
+        ho = torch.empty((heads, dim)).pin_memory()
+        got = a.decode_step(hk, hv, hq, out=ho, pos=cap - 2 + step)
+        b.append_all(k, v)
+        want = b.compute_all(q)
+        assert torch.equal(got, want.cpu()), f"step {step}: pipelined decode step differs from append + compute"
+    assert gpu_lib.adaptq_kernel_launches() > launches0
+    for h in (0, 517, heads - 1):
+        ea, eb = a.export_head(h), b.export_head(h)
+        for key in ("k_rows", "v_rows", "k_scale", "v_scale"):
+            assert np.array_equal(ea[key], eb[key]), (h, key)
+        assert (ea["ring_head"], ea["ring_size"]) == (eb["ring_head"], eb["ring_size"])
+    a.close()
+    b.close()
+
+
+def test_decode_step_argument_errors(gpu_lib):
+    import ctypes as C
+    L = gpu_lib
+    m = C.c_void_p(L.adaptq_mha_create(2, 64, 4, 4, 16, 1, C.c_float(0.0), 0))
+    x = np.ones((2, 64), dtype=np.float32)
+    assert L.adaptq_mha_decode_step(m, None, x.ctypes.data, x.ctypes.data, x.ctypes.data, 0) == -1
+    assert L.adaptq_last_error().decode() == "adaptq_mha_decode_step: null keys"
+    assert L.adaptq_mha_decode_step(m, x.ctypes.data, x.ctypes.data, x.ctypes.data, None, 0) == -1
+    assert L.adaptq_last_error().decode() == "adaptq_mha_decode_step: null outs"
+    assert L.adaptq_mha_decode_step(None, x.ctypes.data, x.ctypes.data, x.ctypes.data, x.ctypes.data, 0) == -1
+    assert L.adaptq_mha_decode_step(m, x.ctypes.data, x.ctypes.data, x.ctypes.data, x.ctypes.data, 0) == 1
+    L.adaptq_mha_destroy(m)

@@ -4,7 +4,8 @@ NVIDIA B200 (sm_100a), behind upstream's own interfaces:
 * the C ABI of include/adaptq.h (+ batched additions in include/adaptq_b200.h),
   implemented by ``libadaptq_b200.so``;
 * ``MHAContext`` (upstream's pybind class ``adaptq_py.MHAContext``);
-* ``Engine`` (upstream ``adaptq.Engine``) and ``AdaptQAttention``.
+* ``Engine`` (upstream ``adaptq.Engine``), ``AdaptQAttention`` and its
+  many-sequence form ``BatchedAdaptQAttention``.
 """
 from ._lib import LIB_PATH, last_error, load  # noqa: F401
 from .core import Engine  # noqa: F401
@@ -14,7 +15,7 @@ __version__ = "0.1.0"
 
 
 def __getattr__(name):
-    if name == "AdaptQAttention":  # lazy: importing torch is slow
-        from .torch_adapter import AdaptQAttention
-        return AdaptQAttention
+    if name in ("AdaptQAttention", "BatchedAdaptQAttention"):  # lazy: importing torch is slow
+        from . import torch_adapter
+        return getattr(torch_adapter, name)
     raise AttributeError(name)

@@ -387,7 +387,11 @@ bool append_device(Group *g, const float *dk, const float *dv, int head0, int he
   a.c = g->c;
   a.head0 = head0; a.heads_in_call = heads_in_call; a.n_tokens = n_tokens;
   a.ring_head = st.head; a.ring_size = st.size; a.mirror_cnt = st.mirror;
-  a.head_major = n_tokens >= 32;
+  // One contiguous block of rows (the call covers whole tokens, no padding): walk it
+  // token-major so that a tile is one stretch of memory; otherwise walk the tokens of
+  // a head so that its packed rows leave in order.
+  a.contig = (token_stride == (size_t)heads_in_call * g->c.dim && g->c.dim == g->c.padded) ? 1 : 0;
+  a.head_major = a.contig ? 0 : (n_tokens >= 32);
   a.status = g->d_status;
   a.src_token_stride = token_stride;
   magic_div((uint32_t)(a.head_major ? n_tokens : heads_in_call), a.div_magic, a.div_shift, a.div_add);

@@ -25,6 +25,7 @@ struct AppendLaunch {
   int head0, heads_in_call, n_tokens;
   int ring_head, ring_size, mirror_cnt; // state shared by the heads of this call
   int head_major;
+  int contig;       // items are token-major and item g starts at src + g*dim (one contiguous block)
   int *status;
   // exact division of 32-bit values by the item divisor (n_tokens when head_major,
   // else heads_in_call) and by the ring capacity: q = umulhi(x, magic) >> shift
@@ -395,6 +396,12 @@ template <int P, int BITS>
 __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kernel(const AppendLaunch a) {
   constexpr int EPL = P / 4;     // coordinates per lane
   constexpr int PITCH = P + 4;   // floats; +16 B keeps both passes' 128-bit reads conflict-free
+  // Contiguous sources arrive eight rows per bulk copy (a copy costs its issuing
+  // thread tens of cycles whatever its size): rows then sit back to back in groups
+  // of eight, with the 16-byte skew between groups instead of between rows, and
+  // both passes pick their rows across groups to keep 128-bit reads conflict-free.
+  constexpr int GROUP = 8, GPITCH = GROUP * P + 4;
+  static_assert(AT_TILE % GROUP == 0 && AT_TILE / GROUP == 8, "eight groups of eight rows");
   constexpr int QB = BITS == 16 ? 4 : BITS;
   extern __shared__ __align__(128) unsigned char smem_rows[];
   float *tile = reinterpret_cast<float *>(smem_rows);
@@ -406,8 +413,14 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
   __shared__ int redo_list[2][AT_TILE];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int vt = warp * 8 + (lane & 7); // vector of the tile this lane works on in pass 2
-  const int part = lane >> 3;           // which quarter of it
+  const bool contig = a.contig != 0;
+  // vector of the tile this lane works on in pass 2, the row thread `tid` sums in pass 1
+  const int vt = contig ? ((lane & 7) * GROUP + warp) : (warp * 8 + (lane & 7));
+  const int row1 = contig ? ((tid & 7) * GROUP + (tid >> 3)) : tid;
+  const int part = lane >> 3;           // which quarter of the vector
+  auto row_ptr = [&](int r) -> float * {
+    return contig ? tile + (size_t)(r >> 3) * GPITCH + (size_t)(r & 7) * P : tile + (size_t)r * PITCH;
+  };
   if constexpr (BITS != 16) build_quant_table<QB>(qtab, tid, AT_THREADS);
   const uint32_t qtab_addr = smem_u32(qtab);
   const CacheView &c = a.c;
@@ -425,7 +438,18 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
     for (int i = dim; i < P; ++i) tile[(size_t)tid * PITCH + i] = 0.f;
   __syncthreads();
 
-  auto issue = [&](long long tile_idx) { // threads 0..127: one row each
+  auto issue = [&](long long tile_idx) { // threads 0..AT_TILE-1: one row each, or eight rows for the first eight
+    if (contig) {
+      const long long g0 = tile_idx * AT_TILE + (long long)tid * GROUP;
+      if (tid < AT_TILE / GROUP && g0 < n_items) {
+        const uint32_t bytes = (uint32_t)min((long long)GROUP, n_items - g0) * row_bytes_in;
+        mbar_expect_tx(&bar, bytes);
+        bulk_g2s(tile + (size_t)tid * GPITCH, a.src + (size_t)g0 * P, bytes, &bar);
+        return;
+      }
+      mbar_arrive(&bar);
+      return;
+    }
     const long long g = tile_idx * AT_TILE + tid;
     if (g < n_items) {
       const ItemPlace p = place_item32(a, (uint32_t)g);
@@ -453,11 +477,11 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
 
     // ---- pass 1: sequential norms (core/quantizer.cpp:59-66), one thread per vector ----
     if (BITS != 16 && tid < AT_TILE) {
-      const long long g = tile_idx * AT_TILE + tid;
+      const long long g = tile_idx * AT_TILE + row1;
       bool live = false;
       if (g < n_items) live = place_item32(a, (uint32_t)g).store;
       if (live) {
-        const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(tile + (size_t)tid * PITCH);
+        const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(row_ptr(row1));
         float sum = 0.f;
 #pragma unroll 8
         for (int i = 0; i < P / 4; ++i) {
@@ -472,10 +496,10 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
         // norm >= 1e-5 makes the +-3 sigma clip a no-op and rules out NaN (see
         // quantize_lookup); an all-zero vector quantises to the middle index either way
         const bool plain = (norm >= 1e-5f && norm < INFINITY) || all_zero;
-        s_norm[tid] = plain ? make_float2(norm, __fdiv_rn(1.0f, norm)) : make_float2(-1.f, 1.f);
-        if (!plain) redo_list[par][atomicAdd(&redo_count[par], 1)] = tid;
+        s_norm[row1] = plain ? make_float2(norm, __fdiv_rn(1.0f, norm)) : make_float2(-1.f, 1.f);
+        if (!plain) redo_list[par][atomicAdd(&redo_count[par], 1)] = row1;
       } else {
-        s_norm[tid] = make_float2(-1.f, 1.f);
+        s_norm[row1] = make_float2(-1.f, 1.f);
       }
     }
 
@@ -504,7 +528,7 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
     unsigned long long xp[EPL / 2]; // coordinates (2i, 2i+1) of this quarter, packed
     {
       const bool have = p.store || p.mirror;
-      const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(tile + (size_t)vt * PITCH + part * EPL);
+      const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(row_ptr(vt) + part * EPL);
 #pragma unroll
       for (int i = 0; i < EPL / 4; ++i) {
         const ulonglong2 v = have ? r2[i] : make_ulonglong2(0ull, 0ull);

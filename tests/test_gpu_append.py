@@ -72,6 +72,12 @@ def test_per_head_calls_equal_batched_calls(gpu_lib, orc):
     cpu.append_many(k[10:40], v[10:40])
     for h in range(heads):
         assert_cache_equal(a.export_head(h), cpu.heads[h], f"head {h} after batched call")
+    # a long batch on the still non-uniform state: per-head launches over strided rows
+    k2, v2 = make_kv(rng, 150, heads, dim)
+    a.append_all(k2, v2)
+    cpu.append_many(k2, v2)
+    for h in range(heads):
+        assert_cache_equal(a.export_head(h), cpu.heads[h], f"head {h} after the long strided batch")
 
 
 def test_special_values(gpu_lib, orc):

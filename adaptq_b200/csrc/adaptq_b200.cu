@@ -336,12 +336,52 @@ bool launch_rows_bits(Group *g, const AppendLaunch &a, int bits) {
   }
 }
 
+// Keys and values together (both quantised): one launch, blockIdx.y = side.
+template <int P, int KB, int VB>
+bool launch_pair(Group *g, const AppendLaunch &ak, const AppendLaunch &av) {
+  constexpr size_t SMEM = ((size_t)AT_TILE * (P + 4) + (size_t)(AT_THREADS / 32) * P) * sizeof(float);
+  static bool configured[64] = {};
+  auto kern = append_pair_kernel<P, KB, VB>;
+  if (!configured[g->device & 63]) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM), "append");
+    configured[g->device & 63] = true;
+  }
+  long long items = (long long)ak.heads_in_call * ak.n_tokens;
+  long long tiles = (items + AT_TILE - 1) / AT_TILE;
+  int gx = (int)std::min<long long>(tiles, (long long)g->sm_count * (AT_BLOCKS_PER_SM / 2));
+  kern<<<dim3(gx, 2), AT_THREADS, SMEM, g->stream>>>(ak, av);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "append");
+  return true;
+}
+template <int P, int KB>
+bool launch_pair_v(Group *g, const AppendLaunch &ak, const AppendLaunch &av, int vb) {
+  switch (vb) {
+  case 2: return launch_pair<P, KB, 2>(g, ak, av);
+  case 3: return launch_pair<P, KB, 3>(g, ak, av);
+  default: return launch_pair<P, KB, 4>(g, ak, av);
+  }
+}
+template <int P>
+bool launch_pair_kv(Group *g, const AppendLaunch &ak, const AppendLaunch &av, int kb, int vb) {
+  switch (kb) {
+  case 2: return launch_pair_v<P, 2>(g, ak, av, vb);
+  case 3: return launch_pair_v<P, 3>(g, ak, av, vb);
+  default: return launch_pair_v<P, 4>(g, ak, av, vb);
+  }
+}
+
+bool tile_kernel_applies(Group *g, const AppendLaunch &a, int src_row_align_ok) {
+  const CacheView &c = g->c;
+  const bool small = (long long)a.heads_in_call * a.n_tokens < (1ll << 31) && (long long)a.ring_head + a.n_tokens < (1ll << 31);
+  return g_policy.load() != 1 && (c.padded == 64 || c.padded == 128) && (c.dim % 4 == 0) && src_row_align_ok && small;
+}
+
 bool launch_append_one(Group *g, AppendLaunch a, int src_row_align_ok) {
   const CacheView &c = g->c;
   const int bits = a.which ? c.v_bits : c.k_bits;
   const int policy = g_policy.load();
-  const bool small = (long long)a.heads_in_call * a.n_tokens < (1ll << 31) && (long long)a.ring_head + a.n_tokens < (1ll << 31);
-  bool fast = policy != 1 && (c.padded == 64 || c.padded == 128) && (c.dim % 4 == 0) && src_row_align_ok && small;
+  const bool fast = tile_kernel_applies(g, a, src_row_align_ok);
   if (fast) return c.padded == 128 ? launch_rows_bits<128>(g, a, bits) : launch_rows_bits<64>(g, a, bits);
   if (policy == 2) { set_error("append: shape not covered by the specialised kernel"); return false; }
   long long items = (long long)a.heads_in_call * a.n_tokens;
@@ -401,11 +441,20 @@ bool append_device(Group *g, const float *dk, const float *dv, int head0, int he
     volatile float isq = 1.0f / sq;
     a.sqrt_p = sq; a.inv_sqrt_p = isq;
   }
+  const int align_k = ((reinterpret_cast<uintptr_t>(dk) & 15) == 0) && (token_stride % 4 == 0);
+  const int align_v = ((reinterpret_cast<uintptr_t>(dv) & 15) == 0) && (token_stride % 4 == 0);
+  if (g->c.k_bits != 16 && g->c.v_bits != 16) {
+    AppendLaunch ak = a, av = a;
+    ak.which = 0; ak.src = dk;
+    av.which = 1; av.src = dv;
+    if (tile_kernel_applies(g, ak, align_k) && tile_kernel_applies(g, av, align_v))
+      return g->c.padded == 128 ? launch_pair_kv<128>(g, ak, av, g->c.k_bits, g->c.v_bits)
+                                : launch_pair_kv<64>(g, ak, av, g->c.k_bits, g->c.v_bits);
+  }
   for (int which = 0; which < 2; ++which) {
     a.which = which;
     a.src = which ? dv : dk;
-    int align_ok = ((reinterpret_cast<uintptr_t>(a.src) & 15) == 0) && (token_stride % 4 == 0);
-    if (!launch_append_one(g, a, align_ok)) return false;
+    if (!launch_append_one(g, a, which ? align_v : align_k)) return false;
   }
   return true;
 }

@@ -392,8 +392,9 @@ __device__ __forceinline__ void quantize_quarter(unsigned long long (&xp)[P / 8]
   }
 }
 
+// The work of one block: tiles block_rank, block_rank + n_blocks, ... of launch `a`.
 template <int P, int BITS>
-__global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kernel(const AppendLaunch a) {
+__device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const int block_rank, const int n_blocks) {
   constexpr int EPL = P / 4;     // coordinates per lane
   constexpr int PITCH = P + 4;   // floats; +16 B keeps both passes' 128-bit reads conflict-free
   // Contiguous sources arrive eight rows per bulk copy (a copy costs its issuing
@@ -462,10 +463,10 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
     mbar_arrive(&bar);
   };
 
-  long long tile_idx = blockIdx.x;
+  long long tile_idx = block_rank;
   if (tile_idx < n_tiles && tid < AT_TILE) issue(tile_idx);
   uint32_t parity = 0;
-  for (; tile_idx < n_tiles; tile_idx += gridDim.x) {
+  for (; tile_idx < n_tiles; tile_idx += n_blocks) {
     // Only the pass-1 warps poll the copy barrier; everyone else learns of the data
     // through the block barrier after pass 1 (a failed wait is flagged, not fatal:
     // all threads must still reach the barriers).
@@ -537,7 +538,7 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
       }
     }
     __syncthreads(); // every quarter is in registers; the tile buffer is free
-    const long long next = tile_idx + gridDim.x;
+    const long long next = tile_idx + n_blocks;
     if (next < n_tiles && tid < AT_TILE) {
       fence_proxy_async();
       issue(next);
@@ -579,6 +580,20 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
       }
     }
   }
+}
+
+template <int P, int BITS>
+__global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kernel(const AppendLaunch a) {
+  append_tile_body<P, BITS>(a, (int)blockIdx.x, (int)gridDim.x);
+}
+
+// Keys and values of one call in a single launch: blockIdx.y picks the side, so
+// the two sides share the SMs from the first cycle to the last and the launch,
+// ramp-up and tail costs are paid once.
+template <int P, int KB, int VB>
+__global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_pair_kernel(const AppendLaunch ak, const AppendLaunch av) {
+  if (blockIdx.y == 0) append_tile_body<P, KB>(ak, (int)blockIdx.x, (int)gridDim.x);
+  else append_tile_body<P, VB>(av, (int)blockIdx.x, (int)gridDim.x);
 }
 
 } // namespace aq

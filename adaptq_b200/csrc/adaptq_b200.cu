@@ -349,7 +349,7 @@ bool launch_pair(Group *g, const AppendLaunch &ak, const AppendLaunch &av) {
   long long items = (long long)ak.heads_in_call * ak.n_tokens;
   long long tiles = (items + AT_TILE - 1) / AT_TILE;
   int gx = (int)std::min<long long>(tiles, (long long)g->sm_count * (AT_BLOCKS_PER_SM / 2));
-  kern<<<dim3(gx, 2), AT_THREADS, SMEM, g->stream>>>(ak, av);
+  kern<<<dim3(gx, 2), AT_THREADS, SMEM, g->stream>>>(ak, av.src);
   ++g_launches;
   CUDA_TRY(cudaGetLastError(), "append");
   return true;

@@ -392,9 +392,12 @@ __device__ __forceinline__ void quantize_quarter(unsigned long long (&xp)[P / 8]
   }
 }
 
-// The work of one block: tiles block_rank, block_rank + n_blocks, ... of launch `a`.
+// The work of one block: tiles block_rank, block_rank + n_blocks, ... of launch `a`,
+// for side `which` (0 keys, 1 values) whose rows start at `src` (these two override
+// a.which / a.src, so that one launch descriptor serves both sides).
 template <int P, int BITS>
-__device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const int block_rank, const int n_blocks) {
+__device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const float *src, const int which,
+                                                 const int block_rank, const int n_blocks) {
   constexpr int EPL = P / 4;     // coordinates per lane
   constexpr int PITCH = P + 4;   // floats; +16 B keeps both passes' 128-bit reads conflict-free
   // Contiguous sources arrive eight rows per bulk copy (a copy costs its issuing
@@ -445,7 +448,7 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const in
       if (tid < AT_TILE / GROUP && g0 < n_items) {
         const uint32_t bytes = (uint32_t)min((long long)GROUP, n_items - g0) * row_bytes_in;
         mbar_expect_tx(&bar, bytes);
-        bulk_g2s(tile + (size_t)tid * GPITCH, a.src + (size_t)g0 * P, bytes, &bar);
+        bulk_g2s(tile + (size_t)tid * GPITCH, src + (size_t)g0 * P, bytes, &bar);
         return;
       }
       mbar_arrive(&bar);
@@ -456,7 +459,7 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const in
       const ItemPlace p = place_item32(a, (uint32_t)g);
       if (p.store || p.mirror) {
         mbar_expect_tx(&bar, row_bytes_in);
-        bulk_g2s(tile + (size_t)tid * PITCH, item_src(a, p), row_bytes_in, &bar);
+        bulk_g2s(tile + (size_t)tid * PITCH, (src + (size_t)p.t * a.src_token_stride + (size_t)(p.h - a.head0) * a.c.dim), row_bytes_in, &bar);
         return;
       }
     }
@@ -514,8 +517,11 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const in
       const int n_redo = redo_count[par];
       if (tid == 0) redo_count[par ^ 1u] = 0; // the other slot was last read before the previous tile's second barrier
       if (n_redo > 0) { // rare: tiny, infinite or NaN norms go through the general routine (it reads the source again)
+        AppendLaunch side = a; // rare path: a private copy with this side's fields
+        side.src = src;
+        side.which = which;
         for (int e = warp; e < n_redo; e += AT_THREADS / 32)
-          append_item_general(a, tile_idx * AT_TILE + redo_list[par][e], redo_buf + (size_t)warp * P, lane);
+          append_item_general(side, tile_idx * AT_TILE + redo_list[par][e], redo_buf + (size_t)warp * P, lane);
       }
     }
     // Vectors that pass 1 handed to the general routine (norm < 0) are skipped here
@@ -545,19 +551,19 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const in
     }
     if (p.mirror) {
       ulonglong2 *m2 = reinterpret_cast<ulonglong2 *>(c.mirror + (size_t)p.h * c.mirror_stride +
-                                                      (size_t)p.slot * 2 * dim + (a.which ? dim : 0) + part * EPL);
+                                                      (size_t)p.slot * 2 * dim + (which ? dim : 0) + part * EPL);
 #pragma unroll
       for (int i = 0; i < EPL / 4; ++i)
         if (part * EPL + 4 * i < dim) m2[i] = make_ulonglong2(xp[2 * i], xp[2 * i + 1]);
     }
     if constexpr (BITS == 16) {
       if (p.store) {
-        uint8_t *slab = a.which ? c.v_slab : c.k_slab;
-        const size_t stride = a.which ? c.v_stride : c.k_stride;
+        uint8_t *slab = which ? c.v_slab : c.k_slab;
+        const size_t stride = which ? c.v_stride : c.k_stride;
         ulonglong2 *dst = reinterpret_cast<ulonglong2 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4)) + part * (EPL / 4);
 #pragma unroll
         for (int i = 0; i < EPL / 4; ++i) dst[i] = make_ulonglong2(xp[2 * i], xp[2 * i + 1]);
-        if (part == 0) ((a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = 1.0f;
+        if (part == 0) ((which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = 1.0f;
       }
     } else {
       // Every lane runs the transform (its shuffles need the whole warp); lanes whose
@@ -573,10 +579,10 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const in
       uint32_t w[(EPL * BITS + 31) / 32];
       quantize_quarter<P, BITS>(xp, keep ? nrm.y : 1.f, a.sqrt_p, a.inv_sqrt_p, sgw, lane, w, qtab_addr);
       if (keep) {
-        uint8_t *slab = a.which ? c.v_slab : c.k_slab;
-        const size_t stride = a.which ? c.v_stride : c.k_stride;
+        uint8_t *slab = which ? c.v_slab : c.k_slab;
+        const size_t stride = which ? c.v_stride : c.k_stride;
         store_packed<NBYTES>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * BITS / 8) + part * NBYTES, w);
-        if (part == 0) ((a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = norm;
+        if (part == 0) ((which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = norm;
       }
     }
   }
@@ -584,16 +590,22 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const in
 
 template <int P, int BITS>
 __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kernel(const AppendLaunch a) {
-  append_tile_body<P, BITS>(a, (int)blockIdx.x, (int)gridDim.x);
+  append_tile_body<P, BITS>(a, a.src, a.which, (int)blockIdx.x, (int)gridDim.x);
 }
 
 // Keys and values of one call in a single launch: blockIdx.y picks the side, so
 // the two sides share the SMs from the first cycle to the last and the launch,
 // ramp-up and tail costs are paid once.
 template <int P, int KB, int VB>
-__global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_pair_kernel(const AppendLaunch ak, const AppendLaunch av) {
-  if (blockIdx.y == 0) append_tile_body<P, KB>(ak, (int)blockIdx.x, (int)gridDim.x);
-  else append_tile_body<P, VB>(av, (int)blockIdx.x, (int)gridDim.x);
+__global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_pair_kernel(const AppendLaunch a, const float *src_v) {
+  // a describes the call and carries the key rows in a.src; the value rows start at src_v
+  if constexpr (KB == VB) { // one copy of the code serves both sides
+    const int which = (int)blockIdx.y;
+    append_tile_body<P, KB>(a, which ? src_v : a.src, which, (int)blockIdx.x, (int)gridDim.x);
+  } else {
+    if (blockIdx.y == 0) append_tile_body<P, KB>(a, a.src, 0, (int)blockIdx.x, (int)gridDim.x);
+    else append_tile_body<P, VB>(a, src_v, 1, (int)blockIdx.x, (int)gridDim.x);
+  }
 }
 
 } // namespace aq

@@ -248,8 +248,8 @@ def append_bench(torch, L, peak):
 
 def latency_bench(torch):
     """Per-token decode latency of the small configurations: one engine per layer
-    (seed 42 ^ layer), per step and layer one append of the new token and one
-    attention call, device tensors in place.  These shapes move 0.5-25 MB per
+    (seed 42 ^ layer), per step and layer one decode-step call (append of the new
+    token + attention), device tensors in place.  These shapes move 0.5-25 MB per
     step, so they are launch/latency bound; the figure of merit is us per token."""
     import numpy as np
     import adaptq_b200
@@ -276,8 +276,7 @@ def latency_bench(torch):
 
         def step():
             for l, e in enumerate(engines):
-                e.append_all(kn[l], kn[l])
-                e.compute_all(q[l], out=o[l])
+                e.decode_step(kn[l], kn[l], q[l], out=o[l])
         for _ in range(5):
             step()
         torch.cuda.synchronize()

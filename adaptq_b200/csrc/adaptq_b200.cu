@@ -481,7 +481,7 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   const bool v_f32 = mirror || c.v_bits == 16;
   const int items = a.heads_in_call * a.nq;
   int want = std::max(1, (2 * g->sm_count + items - 1) / items);
-  int max_splits = std::max(1, (a.n + 255) / 256);
+  int max_splits = std::max(1, (a.n + 63) / 64); // short spans: these shapes are latency-bound, so spread them wide
   a.n_splits = std::min(want, max_splits);
   a.span = (int)round_up((size_t)(a.n + a.n_splits - 1) / a.n_splits, 32);
   a.n_splits = (a.n + a.span - 1) / a.span;

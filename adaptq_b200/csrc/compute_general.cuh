@@ -116,6 +116,7 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   for (int t0 = t_begin; t0 < t_end; t0 += a.chunk) {
     const int cn = min(a.chunk, t_end - t0);
     // ---- scores ----------------------------------------------------------
+#pragma unroll 4
     for (int i = warp; i < cn; i += CG_WARPS) {
       const int s = t0 + i;
       float sum = 0.f;
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
       const int j = jcol + r * CG_THREADS;
       if (j >= P || (P < CG_THREADS && r > 0)) break;
       float av = acc[r] * rescale;
+#pragma unroll 4
       for (int i = tg; i < cn; i += TG) {
         const int s = t0 + i;
         if (v_f32) {

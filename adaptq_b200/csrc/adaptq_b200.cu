@@ -77,7 +77,9 @@ struct Group {
   // device staging for host-pointer calls, and scratch for partials / sparse V
   void *d_stage = nullptr; size_t stage_bytes = 0;
   void *h_stage = nullptr; size_t h_stage_bytes = 0;
+  void *d_scratch_base = nullptr; // header + scratch, one allocation
   void *d_scratch = nullptr; size_t scratch_bytes = 0;
+  int *d_counters = nullptr;
   int *d_status = nullptr;
   size_t device_bytes = 0;
   std::mutex mu;
@@ -131,7 +133,7 @@ void free_group(Group *g) {
   if (g->stream == nullptr || true) cudaDeviceSynchronize();
   cudaFree(g->c.k_slab); cudaFree(g->c.v_slab); cudaFree(g->c.k_scale); cudaFree(g->c.v_scale);
   cudaFree((void *)g->c.signs); cudaFree(g->c.mirror);
-  cudaFree(g->d_stage); cudaFree(g->d_scratch); cudaFree(g->d_status);
+  cudaFree(g->d_stage); cudaFree(g->d_scratch_base); cudaFree(g->d_status);
   if (g->h_stage) cudaFreeHost(g->h_stage);
   if (g->copy_in) cudaStreamDestroy(g->copy_in);
   if (g->copy_out) cudaStreamDestroy(g->copy_out);
@@ -262,13 +264,20 @@ bool ensure_stage(Group *g, size_t dev_bytes, size_t host_bytes) {
   return true;
 }
 
+// Scratch = a zeroed header of arrival counters (kernels that use them leave them at
+// zero) followed by the space for partials / sparse-V work arrays.
+constexpr size_t SCRATCH_HEADER = 65536;
+constexpr int MAX_COUNTED_ITEMS = (int)(SCRATCH_HEADER / sizeof(int));
 bool ensure_scratch(Group *g, size_t bytes) {
   if (bytes <= g->scratch_bytes) return true;
   CUDA_TRY(cudaStreamSynchronize(g->stream), "scratch");
-  if (g->d_scratch) { cudaFree(g->d_scratch); g->device_bytes -= g->scratch_bytes; }
-  g->d_scratch = nullptr; g->scratch_bytes = 0;
+  if (g->d_scratch_base) { cudaFree(g->d_scratch_base); g->device_bytes -= g->scratch_bytes + SCRATCH_HEADER; }
+  g->d_scratch_base = nullptr; g->d_scratch = nullptr; g->d_counters = nullptr; g->scratch_bytes = 0;
   size_t nb = round_up(bytes + bytes / 4, 256);
-  if (!alloc(&g->d_scratch, nb, g, "scratch")) return false;
+  if (!alloc(&g->d_scratch_base, nb + SCRATCH_HEADER, g, "scratch")) return false;
+  CUDA_TRY(cudaMemsetAsync(g->d_scratch_base, 0, SCRATCH_HEADER, g->stream), "scratch");
+  g->d_counters = static_cast<int *>(g->d_scratch_base);
+  g->d_scratch = static_cast<char *>(g->d_scratch_base) + SCRATCH_HEADER;
   g->scratch_bytes = nb;
   return true;
 }
@@ -497,11 +506,16 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   } else {
     a.mode = 0;
   }
+  // few items: the last block to finish an item merges its partials inside the same launch
+  const bool fused = !direct && items <= MAX_COUNTED_ITEMS;
+  a.counters = fused ? g->d_counters : nullptr;
+  a.final_out = want_partial_out ? partial_out : a.out;
+  a.final_to_partial = want_partial_out ? 1 : 0;
   dim3 grid(a.n_splits, a.heads_in_call, a.nq);
   compute_general_kernel<<<grid, CG_THREADS, smem, g->stream>>>(a);
   ++g_launches;
   CUDA_TRY(cudaGetLastError(), "compute");
-  if (!direct) {
+  if (!direct && !fused) {
     merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
         a.partial, (size_t)items * partial_floats(c), a.n_splits, c, a.head0, a.nq,
         want_partial_out ? partial_out : a.out, v_f32 ? 1 : 0, want_partial_out ? 1 : 0);

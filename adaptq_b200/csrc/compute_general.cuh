@@ -32,6 +32,10 @@ struct ComputeLaunch {
   int n_splits, span; // tokens per split
   int chunk;          // tokens per shared-memory pass
   int mode;
+  // mode 1 with fused merge: the block that completes an item's last partial merges them
+  int *counters;      // [heads_in_call*nq] arrival counts, zero before and after every launch (nullptr: no fused merge)
+  float *final_out;   // outputs (or combined partials when final_to_partial)
+  int final_to_partial;
 };
 
 // Shared-memory carve-up (floats): qr[P] | vec[P] | red[64] | lut[P*CBK or 0] | sc[chunk]
@@ -48,6 +52,110 @@ __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) 
   float r = red[0];
   for (int i = 1; i < CG_WARPS; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
   return r;
+}
+
+// Merge n_parts split-KV partials per (head, query): rescale to the common
+// max, sum, normalise, one inverse transform.  parts laid out
+// [n_parts][items][2+P] with part stride `part_stride` floats.
+// One block (CG_THREADS threads) merges the n_parts partials of `item`; vec: P floats of shared memory.
+// Partials are read past L1 (__ldcg): other blocks of the same launch may have written them.
+__device__ __forceinline__ void merge_partials_block(const float *parts, size_t part_stride, int n_parts, const CacheView &c,
+                                                     int item, int h, float *out, int v_f32, int to_partial, float *vec) {
+  const int P = c.padded, dim = c.dim;
+  const int tid = threadIdx.x;
+  const float *base = parts + (size_t)item * (2 + P);
+  // All loads of a step are independent of each other, so their latencies
+  // overlap: the (max, sum) pairs are read one part per thread, the
+  // accumulators with the parts dealt round-robin to thread groups.
+  __shared__ float s_w[1024];        // weight exp(m_p - M) of the first 1024 parts
+  __shared__ float s_red[CG_WARPS];
+  __shared__ float s_grp[CG_THREADS];
+  const int lane = tid & 31, warp = tid >> 5;
+  float m_loc = -INFINITY;
+  for (int p = tid; p < n_parts; p += CG_THREADS) {
+    const float *pp = base + (size_t)p * part_stride;
+    if (__ldcg(pp + 1) > 0.f) m_loc = fmaxf(m_loc, __ldcg(pp));
+  }
+  m_loc = warp_max(m_loc);
+  if (lane == 0) s_red[warp] = m_loc;
+  __syncthreads();
+  float M = s_red[0];
+  for (int w = 1; w < CG_WARPS; ++w) M = fmaxf(M, s_red[w]);
+  __syncthreads();
+  float l_loc = 0.f;
+  for (int p = tid; p < n_parts; p += CG_THREADS) {
+    const float *pp = base + (size_t)p * part_stride;
+    const float l = __ldcg(pp + 1);
+    const float w = l > 0.f ? expf(__ldcg(pp) - M) : 0.f;
+    if (p < 1024) s_w[p] = w;
+    l_loc += l > 0.f ? l * w : 0.f;
+  }
+  l_loc = warp_sum(l_loc);
+  if (lane == 0) s_red[warp] = l_loc;
+  __syncthreads(); // also publishes s_w
+  float L = 0.f;
+  for (int w = 0; w < CG_WARPS; ++w) L += s_red[w];
+  const float invL = to_partial ? 1.f : 1.f / L;
+  auto weight = [&](int p) -> float {
+    if (p < 1024) return s_w[p];
+    const float *pp = base + (size_t)p * part_stride;
+    return __ldcg(pp + 1) > 0.f ? expf(__ldcg(pp) - M) : 0.f;
+  };
+  if (P <= CG_THREADS) {
+    const int groups = CG_THREADS / P, g = tid / P, j = tid % P;
+    float s = 0.f;
+    if (g < groups) {
+#pragma unroll 8
+      for (int p = g; p < n_parts; p += groups) {
+        const float w = weight(p);
+        const float v = w > 0.f ? __ldcg(base + (size_t)p * part_stride + 2 + j) : 0.f;
+        s += v * w;
+      }
+    }
+    s_grp[tid] = s;
+    __syncthreads();
+    if (tid < P) {
+      float t = 0.f;
+      for (int gg = 0; gg < groups; ++gg) t += s_grp[gg * P + tid];
+      vec[tid] = t * invL;
+    }
+  } else {
+    for (int j = tid; j < P; j += CG_THREADS) {
+      float s = 0.f;
+#pragma unroll 8
+      for (int p = 0; p < n_parts; ++p) {
+        const float w = weight(p);
+        const float v = w > 0.f ? __ldcg(base + (size_t)p * part_stride + 2 + j) : 0.f;
+        s += v * w;
+      }
+      vec[j] = s * invL;
+    }
+  }
+  __syncthreads();
+  if (to_partial) { // one combined, still un-normalised partial per (head, query)
+    float *po = out + (size_t)item * (2 + P);
+    if (tid == 0) { po[0] = M; po[1] = L; }
+    for (int j = tid; j < P; j += CG_THREADS) po[2 + j] = vec[j];
+    return;
+  }
+  float *o = out + (size_t)item * dim;
+  if (v_f32) {
+    for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j];
+    return;
+  }
+  block_butterflies(vec, P);
+  const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
+  const float isp = 1.f / sqrtf((float)P);
+  for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
+}
+
+__global__ void __launch_bounds__(CG_THREADS) merge_partials_kernel(
+    const float *parts, size_t part_stride, int n_parts, CacheView c, int head0, int nq, float *out,
+    int v_f32, int to_partial) {
+  extern __shared__ __align__(16) unsigned char smem_gen[];
+  const int item = blockIdx.x; // hl*nq + qi
+  merge_partials_block(parts, part_stride, n_parts, c, item, head0 + item / nq, out, v_f32, to_partial,
+                       reinterpret_cast<float *>(smem_gen));
 }
 
 __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const ComputeLaunch a) {
@@ -199,9 +307,23 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   __syncthreads();
 
   if (a.mode == 1) {
-    float *pp = a.partial + ((size_t)split * a.heads_in_call * a.nq + (size_t)hl * a.nq + qi) * (size_t)(2 + P);
+    const int item = hl * a.nq + qi;
+    const size_t part_stride = (size_t)a.heads_in_call * a.nq * (size_t)(2 + P);
+    float *pp = a.partial + (size_t)split * part_stride + (size_t)item * (size_t)(2 + P);
     if (tid == 0) { pp[0] = run_m; pp[1] = run_l; }
     for (int j = tid; j < P; j += CG_THREADS) pp[2 + j] = vec[j];
+    if (a.counters == nullptr) return;
+    // The block that brings an item's count to n_splits merges its partials (no block
+    // ever waits for another one); it also puts the count back to zero for the next launch.
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&a.counters[item], 1) == a.n_splits - 1 ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    if (tid == 0) a.counters[item] = 0;
+    __threadfence();
+    merge_partials_block(a.partial, part_stride, a.n_splits, c, item, h, a.final_out, v_f32 ? 1 : 0, a.final_to_partial, vec);
     return;
   }
   // ---- normalise, inverse transform, write ----------------------------------------
@@ -214,105 +336,6 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   for (int j = tid; j < P; j += CG_THREADS) vec[j] *= invl;
   __syncthreads();
   block_butterflies(vec, P);
-  for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
-}
-
-// Merge n_parts split-KV partials per (head, query): rescale to the common
-// max, sum, normalise, one inverse transform.  parts laid out
-// [n_parts][items][2+P] with part stride `part_stride` floats.
-__global__ void __launch_bounds__(CG_THREADS) merge_partials_kernel(
-    const float *parts, size_t part_stride, int n_parts, CacheView c, int head0, int nq, float *out,
-    int v_f32, int to_partial) {
-  extern __shared__ __align__(16) unsigned char smem_gen[];
-  unsigned char *smem_raw = smem_gen;
-  float *vec = reinterpret_cast<float *>(smem_raw);
-  const int P = c.padded, dim = c.dim;
-  const int item = blockIdx.x; // hl*nq + qi
-  const int h = head0 + item / nq;
-  const int tid = threadIdx.x;
-  const float *base = parts + (size_t)item * (2 + P);
-  // All loads of a step are independent of each other, so their latencies
-  // overlap: the (max, sum) pairs are read one part per thread, the
-  // accumulators with the parts dealt round-robin to thread groups.
-  __shared__ float s_w[1024];        // weight exp(m_p - M) of the first 1024 parts
-  __shared__ float s_red[CG_WARPS];
-  __shared__ float s_grp[CG_THREADS];
-  const int lane = tid & 31, warp = tid >> 5;
-  float m_loc = -INFINITY;
-  for (int p = tid; p < n_parts; p += CG_THREADS) {
-    const float *pp = base + (size_t)p * part_stride;
-    if (pp[1] > 0.f) m_loc = fmaxf(m_loc, pp[0]);
-  }
-  m_loc = warp_max(m_loc);
-  if (lane == 0) s_red[warp] = m_loc;
-  __syncthreads();
-  float M = s_red[0];
-  for (int w = 1; w < CG_WARPS; ++w) M = fmaxf(M, s_red[w]);
-  __syncthreads();
-  float l_loc = 0.f;
-  for (int p = tid; p < n_parts; p += CG_THREADS) {
-    const float *pp = base + (size_t)p * part_stride;
-    const float l = pp[1];
-    const float w = l > 0.f ? expf(pp[0] - M) : 0.f;
-    if (p < 1024) s_w[p] = w;
-    l_loc += l > 0.f ? l * w : 0.f;
-  }
-  l_loc = warp_sum(l_loc);
-  if (lane == 0) s_red[warp] = l_loc;
-  __syncthreads(); // also publishes s_w
-  float L = 0.f;
-  for (int w = 0; w < CG_WARPS; ++w) L += s_red[w];
-  const float invL = to_partial ? 1.f : 1.f / L;
-  auto weight = [&](int p) -> float {
-    if (p < 1024) return s_w[p];
-    const float *pp = base + (size_t)p * part_stride;
-    return pp[1] > 0.f ? expf(pp[0] - M) : 0.f;
-  };
-  if (P <= CG_THREADS) {
-    const int groups = CG_THREADS / P, g = tid / P, j = tid % P;
-    float s = 0.f;
-    if (g < groups) {
-#pragma unroll 8
-      for (int p = g; p < n_parts; p += groups) {
-        const float w = weight(p);
-        const float v = w > 0.f ? base[(size_t)p * part_stride + 2 + j] : 0.f;
-        s += v * w;
-      }
-    }
-    s_grp[tid] = s;
-    __syncthreads();
-    if (tid < P) {
-      float t = 0.f;
-      for (int gg = 0; gg < groups; ++gg) t += s_grp[gg * P + tid];
-      vec[tid] = t * invL;
-    }
-  } else {
-    for (int j = tid; j < P; j += CG_THREADS) {
-      float s = 0.f;
-#pragma unroll 8
-      for (int p = 0; p < n_parts; ++p) {
-        const float w = weight(p);
-        const float v = w > 0.f ? base[(size_t)p * part_stride + 2 + j] : 0.f;
-        s += v * w;
-      }
-      vec[j] = s * invL;
-    }
-  }
-  __syncthreads();
-  if (to_partial) { // one combined, still un-normalised partial per (head, query)
-    float *po = out + (size_t)item * (2 + P);
-    if (tid == 0) { po[0] = M; po[1] = L; }
-    for (int j = tid; j < P; j += CG_THREADS) po[2 + j] = vec[j];
-    return;
-  }
-  float *o = out + (size_t)item * dim;
-  if (v_f32) {
-    for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j];
-    return;
-  }
-  block_butterflies(vec, P);
-  const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
-  const float isp = 1.f / sqrtf((float)P);
   for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
 }
 

@@ -7,6 +7,7 @@
 #include "../../include/adaptq_b200.h"
 #include "append.cuh"
 #include "compute_general.cuh"
+#include "compute_sparse.cuh"
 #include "compute_stream.cuh"
 
 #include <algorithm>
@@ -525,12 +526,52 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   return true;
 }
 
+// Logits of every (head, query) into w[items][ws] with the general kernel (mode 2).
+bool launch_logits(Group *g, ComputeLaunch &a, float *w, int ws) {
+  const CacheView &c = g->c;
+  const int items = a.heads_in_call * a.nq;
+  a.weights = w; a.w_stride = ws; a.mode = 2;
+  a.n_splits = std::max(1, std::min((2 * g->sm_count + items - 1) / items, (a.n + 63) / 64));
+  a.span = (int)round_up((size_t)(a.n + a.n_splits - 1) / a.n_splits, 32);
+  a.n_splits = (a.n + a.span - 1) / a.span;
+  a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
+  size_t smem = cg_smem_floats(c.padded, 1 << c.k_bits, a.chunk) * sizeof(float);
+  if (!ensure_general_smem(g, smem)) return false;
+  compute_general_kernel<<<dim3(a.n_splits, a.heads_in_call, a.nq), CG_THREADS, smem, g->stream>>>(a);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "compute (logits)");
+  return true;
+}
+
+template <int ITEMS>
+bool launch_sparse_fused_t(Group *g, const ComputeLaunch &a, const float *w, int ws) {
+  const size_t smem = SparseSmem<ITEMS>::bytes;
+  static bool configured[64] = {};
+  auto kern = sparse_fused_kernel<ITEMS>;
+  if (!configured[g->device & 63]) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute (sparse V)");
+    configured[g->device & 63] = true;
+  }
+  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, g->c, a.head0, a.nq, a.out);
+  ++g_launches;
+  CUDA_TRY(cudaGetLastError(), "compute (sparse V)");
+  return true;
+}
+
 bool launch_sparse(Group *g, ComputeLaunch &a) {
   const CacheView &c = g->c;
   const int items = a.heads_in_call * a.nq;
   const int ws = (int)round_up((size_t)a.n, 32);
   const size_t cells = (size_t)items * ws;
   if (cells > (size_t)0x7fffffff) { set_error("compute: sparse-V workspace too large for one call"); return false; }
+  if (a.n <= SP_THREADS * 16) { // one block per (head, query) sorts and accumulates in shared memory
+    if (!ensure_scratch(g, cells * 4 + 256)) return false;
+    float *w = static_cast<float *>(g->d_scratch);
+    if (!launch_logits(g, a, w, ws)) return false;
+    if (a.n <= SP_THREADS * 4) return launch_sparse_fused_t<4>(g, a, w, ws);
+    if (a.n <= SP_THREADS * 8) return launch_sparse_fused_t<8>(g, a, w, ws);
+    return launch_sparse_fused_t<16>(g, a, w, ws);
+  }
   size_t temp_bytes = 0;
   cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
                                                      (const int *)nullptr, (int *)nullptr, (int)cells, items,
@@ -544,18 +585,11 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
   int *o = (int *)(base + off_o), *so = (int *)(base + off_so);
   int *sb = (int *)(base + off_b), *se = (int *)(base + off_e);
   // 1. logits into the weight buffer (general kernel, mode 2)
-  a.weights = w; a.w_stride = ws; a.mode = 2;
-  a.n_splits = std::max(1, std::min((2 * g->sm_count + items - 1) / items, (a.n + 255) / 256));
-  a.span = (int)round_up((size_t)(a.n + a.n_splits - 1) / a.n_splits, 32);
-  a.n_splits = (a.n + a.span - 1) / a.span;
-  a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
-  size_t smem = cg_smem_floats(c.padded, 1 << c.k_bits, a.chunk) * sizeof(float);
-  if (!ensure_general_smem(g, smem)) return false;
-  compute_general_kernel<<<dim3(a.n_splits, a.heads_in_call, a.nq), CG_THREADS, smem, g->stream>>>(a);
+  if (!launch_logits(g, a, w, ws)) return false;
   // 2. softmax weights, 3. stable descending sort per (head, query), 4. cut + accumulate
   softmax_weights_kernel<<<items, CG_THREADS, 0, g->stream>>>(w, o, ws, a.n);
   segment_offsets_kernel<<<(items + 255) / 256, 256, 0, g->stream>>>(sb, se, items, ws, a.n);
-  g_launches += 3;
+  g_launches += 2;
   cudaError_t e = cub::DeviceSegmentedRadixSort::SortPairsDescending(base + off_t, temp_bytes, w, sw, o, so, (int)cells,
                                                                      items, sb, se, 0, 32, g->stream);
   g_launches += 1;

@@ -64,7 +64,9 @@ def sparse_cut(weights, v_mass):
     return ii, float(mass)
 
 
-@pytest.mark.parametrize("dim,kb,vb,T,vm", [(64, 4, 2, 2048, 0.95), (128, 4, 4, 700, 0.7), (64, 3, 2, 333, 0.5)])
+@pytest.mark.parametrize("dim,kb,vb,T,vm", [(64, 4, 2, 2048, 0.95), (128, 4, 4, 700, 0.7), (64, 3, 2, 333, 0.5),
+                                            # 4096- and 8192-token block sorts, and the device-wide sort beyond
+                                            (128, 4, 2, 3000, 0.9), (64, 2, 2, 6000, 0.95), (64, 4, 2, 9000, 0.9)])
 def test_sparse_v_matches_oracle(gpu_lib, orc, dim, kb, vb, T, vm):
     """Engine defaults past the hybrid window (BASELINE config 1 'as-is').  The cut
     is found in blocks of four rows, so a query whose running mass lands within

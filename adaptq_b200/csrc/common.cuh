@@ -64,27 +64,6 @@ struct CacheView {
   float v_mass;
 };
 
-struct AppendArgs {
-  CacheView c;
-  const float *keys, *vals; // [n_tokens][heads_in_call][dim]
-  int head0;                // first head of this call
-  int heads_in_call;
-  int n_tokens;
-  int head_major;           // 1: consecutive work items walk tokens of one head
-};
-
-struct ComputeArgs {
-  CacheView c;
-  const float *q; // [heads_in_call][nq][dim]
-  float *out;     // [heads_in_call][nq][dim]
-  float *partial; // [heads_in_call][nq][n_splits][2+padded] (split or partial mode)
-  float *weights; // sparse-V scratch: [heads_in_call][nq][cap]
-  int head0, heads_in_call, nq;
-  int n_splits, chunk; // tokens per split
-  int mode;            // 0 = write outs, 1 = write partials
-  int *status;         // device error word
-};
-
 __host__ __device__ inline int row_bytes(int padded, int bits) {
   return bits == 16 ? padded * 4 : (padded * bits + 7) / 8;
 }

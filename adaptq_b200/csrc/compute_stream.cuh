@@ -8,9 +8,11 @@
 //
 //  * persistent blocks, one per SM; a work item is (head, query, KV span);
 //  * a producer warp feeds a ring of 16 KB shared-memory stages with bulk
-//    (TMA) copies, first the span's K rows, then its V rows -- K and V are
-//    separate slabs and are read as separate streams; the producer runs ahead
-//    across phase and item boundaries so HBM never waits for arithmetic;
+//    (TMA) copies: the span's K rows (each stage with its tokens' K scales),
+//    then its V scales, then its V rows -- K and V are separate slabs and are
+//    read as separate streams; the producer runs ahead across phase and item
+//    boundaries so HBM never waits for arithmetic, and no consumer loop holds
+//    a global load;
 //  * K scoring never unpacks an index: a table T[byte][column] =
 //    sum over the 2 (4-bit) or 4 (2-bit) coordinates packed in that byte of
 //    q_rot[coord]*centroid is built once per item; a score is the sum of one
@@ -40,12 +42,10 @@
 #pragma once
 #include "common.cuh"
 
-#ifndef AQ_COMPACT_BUCKETS
-#define AQ_COMPACT_BUCKETS 1
-#endif
-
 namespace aq {
 
+// -DAQ_PROBE=1 builds a diagnostic variant that accumulates per-phase cycle counts
+// (thread 0 of each block) into StreamLaunch::probe; 2 adds per-wait timing.
 #ifdef AQ_PROBE
 #define AQ_MARK(k)                                     \
   if (tid == 0) {                                      \
@@ -93,6 +93,18 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
 }
 __device__ __forceinline__ void red_shared_add(uint32_t addr, uint32_t v) {
   asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// exp(x) for x <= 0 from the hardware 2^t unit, with the rounding error of
+// t = x*log2(e) (and the part of log2(e) a float cannot hold) put back through
+// exp(x) = 2^t * (1 + r*ln 2): relative error ~2^-22, a third of the instructions of expf.
+__device__ __forceinline__ float exp_nonpos(float x) {
+  const float L2E_HI = 1.4426950216293335f, L2E_LO = 1.9259629911266175e-8f;
+  const float t = x * L2E_HI;
+  const float r = fmaf(x, L2E_HI, -t) + x * L2E_LO;
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+  return fmaf(e, r * 0.6931471805599453f, e);
 }
 
 // Block-wide reductions over the consumer threads with ONE barrier each.  The
@@ -211,7 +223,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   constexpr int KWPL = KW / KLPT, VWPL = VW / 8;                            // words per lane
   constexpr int KC = KW * 4, VC = VW * 4;                                   // byte columns
   constexpr int KE = 8 / KB, VE = 8 / VB;                                   // coordinates per byte
-  constexpr bool COMPACT = AQ_COMPACT_BUCKETS && VC == 32;
+  // 32 byte columns (2-bit V at dim 128, 4-bit at dim 64): bucket rows of 32 columns (128 bytes),
+  // which leaves room for two more ring stages; the address is formed doubled and shifted back
+  constexpr bool COMPACT = VC == 32;
   constexpr int BUCKET_BYTES = COMPACT ? 32768 : CS_TABLE_BYTES;           // [256][32 or 64] 32-bit buckets
 
   extern __shared__ __align__(1024) unsigned char smem_stream[];
@@ -440,9 +454,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   const int krot = KLPT == 4 ? (KW == 16 ? (kg & 1) + 2 * (kg >> 2) : (kg & 3)) : tq;
 #pragma unroll
   for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
-  // With 32 byte columns (2-bit V at dim 128, 4-bit at dim 64) the 64-column rows
-  // hold two copies of the buckets; the upper half of the warps uses the second.
-  const int vcol_off = (VC == 32 && !COMPACT && warp >= CS_WARPS / 2) ? 32 : 0;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int kk = (k + tq) & 3;
@@ -456,7 +467,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // bits 8..15 with one byte-permute
     for (int m = 0; m < VWPL; ++m)
       vconst[m][k] = COMPACT ? ((bucket_addr << 1) | (uint32_t)((4 * vword[m] + kk) << 3))
-                             : (bucket_addr | (uint32_t)((4 * vword[m] + kk + vcol_off) << 2));
+                             : (bucket_addr | (uint32_t)((4 * vword[m] + kk) << 2));
   }
   float *table = reinterpret_cast<float *>(table_p);
   const float *kcb = c_cb[KB - 2];
@@ -648,7 +659,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     float ls = 0.f, wsum = 0.f;
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
-      const float e = expf(sv[r] - mx); // exp(-inf) = 0 for the padding
+      const float e = tid + r * CS_CONSUMERS < len ? exp_nonpos(sv[r] - mx) : 0.f; // padding weighs nothing
       ls += e;
       sv[r] = e * vv[r] * isp;
       wsum += sv[r];
@@ -664,12 +675,13 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // needs from a tile (tokens 4s + tq of its warp's slice) sit side by side, so the
     // lane fetches them with 128-bit loads.
     constexpr int TPWV = TVN / CS_WARPS;
+    static_assert(CS_CONSUMERS % TPWV == 0, "a thread's tokens share their place in the warp slice");
+    const int rem = tid % TPWV;
+    const int shift = (rem & 3) * VSTEPS + (rem >> 2) - rem; // the same for all of this thread's tokens
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
       const int i = tid + r * CS_CONSUMERS;
-      const int rem = i % TPWV;
-      const int pos = i - rem + (rem & 3) * VSTEPS + (rem >> 2);
-      if (i < len_pad) scu[pos] = __float2uint_rn(sv[r] * fx);
+      if (i < len_pad) scu[i + shift] = __float2uint_rn(sv[r] * fx);
     }
     consumer_sync();
 
@@ -746,10 +758,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         } else {
           bi = bucket[b * 64 + col];
           bucket[b * 64 + col] = 0u;
-          if (VC == 32) {
-            bi += bucket[b * 64 + 32 + col];
-            bucket[b * 64 + 32 + col] = 0u;
-          }
         }
         const float bv = (float)bi;
 #pragma unroll

@@ -674,6 +674,10 @@ bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, flo
   }
   const int force_partial = (!direct && a.n_splits == 1) ? 1 : 0;
   a.force_partial = force_partial;
+  const bool fused = a.n_splits > 1 && items_base <= MAX_COUNTED_ITEMS;
+  a.counters = fused ? g->d_counters : nullptr;
+  a.final_out = want_partial_out ? partial_out : a.out;
+  a.final_to_partial = want_partial_out ? 1 : 0;
   const long long items = (long long)items_base * a.n_splits;
   const int grid = (int)std::min<long long>(items, g->sm_count);
   bool ok;
@@ -686,7 +690,7 @@ bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, flo
     ok = launch_stream_t<4, 8, 4, 8>(g, a, grid);
   }
   if (!ok) return false;
-  if (a.n_splits > 1) {
+  if (a.n_splits > 1 && !fused) {
     merge_partials_kernel<<<items_base, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
         a.partial, (size_t)items_base * partial_floats(c), a.n_splits, c, a.head0, a.nq,
         want_partial_out ? partial_out : a.out, 0, want_partial_out ? 1 : 0);

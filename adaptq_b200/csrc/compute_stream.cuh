@@ -78,6 +78,11 @@ struct StreamLaunch {
   int n, n_splits, span; // span: tokens per split, multiple of 64
   int force_partial;     // write the partial even when there is a single span
   int *status;
+  // n_splits > 1 with fused merge: the helper warp that completes a (head, query)'s last
+  // span merges all of them inside the launch
+  int *counters;         // [heads_in_call*nq] arrival counts, zero before and after every launch (nullptr: no fused merge)
+  float *final_out;      // outputs, or combined partials when final_to_partial
+  int final_to_partial;
 #ifdef AQ_PROBE
   unsigned long long *probe; // per-phase cycle counters (diagnostic builds only)
 #endif
@@ -115,10 +120,11 @@ __device__ __forceinline__ float consumer_max(float v, float *red) {
   v = warp_max(v);
   if (lane == 0) red[warp] = v;
   consumer_sync();
-  float r = red[0];
-#pragma unroll
-  for (int i = 1; i < CS_WARPS; ++i) r = fmaxf(r, red[i]);
-  return r;
+  static_assert(CS_WARPS == 16, "four 128-bit reads cover the per-warp values");
+  const float4 *r4 = reinterpret_cast<const float4 *>(red);
+  const float4 a = r4[0], b = r4[1], c = r4[2], d = r4[3];
+  return fmaxf(fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w))),
+               fmaxf(fmaxf(fmaxf(c.x, c.y), fmaxf(c.z, c.w)), fmaxf(fmaxf(d.x, d.y), fmaxf(d.z, d.w))));
 }
 __device__ __forceinline__ void consumer_sum2(float &a, float &b, float *red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -126,10 +132,16 @@ __device__ __forceinline__ void consumer_sum2(float &a, float &b, float *red) {
   b = warp_sum(b);
   if (lane == 0) { red[warp] = a; red[32 + warp] = b; }
   consumer_sync();
-  a = red[0];
-  b = red[32];
+  // the same left-to-right order in every thread, so all threads hold identical sums
+  const float4 *r4 = reinterpret_cast<const float4 *>(red);
+  a = 0.f;
+  b = 0.f;
 #pragma unroll
-  for (int i = 1; i < CS_WARPS; ++i) { a += red[i]; b += red[32 + i]; }
+  for (int i = 0; i < CS_WARPS / 4; ++i) {
+    const float4 x = r4[i], y = r4[8 + i];
+    a = (((a + x.x) + x.y) + x.z) + x.w;
+    b = (((b + y.x) + y.y) + y.z) + y.w;
+  }
 }
 
 // Walsh-Hadamard butterflies over P = 32*EPL values held EPL per lane (lane l
@@ -418,6 +430,69 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         if (lane == 0) { pp[0] = mx; pp[1] = ls; }
 #pragma unroll
         for (int e = 0; e < EPL; ++e) pp[2 + EPL * lane + e] = v[e];
+        if (a.counters != nullptr && a.n_splits > 1) {
+          // Whoever brings the count to n_splits merges (nobody waits for anybody) and
+          // puts the count back to zero for the next launch.
+          __threadfence();
+          __syncwarp();
+          int ticket = 0;
+          if (lane == 0) ticket = atomicAdd(&a.counters[hq], 1);
+          ticket = __shfl_sync(0xffffffffu, ticket, 0);
+          if (ticket == a.n_splits - 1) {
+            if (lane == 0) a.counters[hq] = 0;
+            __threadfence();
+            const size_t pstride = (size_t)items_base * (size_t)(2 + P);
+            const float *base = a.partial + (size_t)hq * (size_t)(2 + P);
+            float M = -INFINITY;
+            for (int p = lane; p < a.n_splits; p += 32) {
+              const float *q2 = base + (size_t)p * pstride;
+              if (__ldcg(q2 + 1) > 0.f) M = fmaxf(M, __ldcg(q2));
+            }
+            M = warp_max(M);
+            float L = 0.f, am[EPL];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) am[e] = 0.f;
+            for (int p0 = 0; p0 < a.n_splits; p0 += 32) {
+              const int p = p0 + lane;
+              float w = 0.f;
+              if (p < a.n_splits) {
+                const float *q2 = base + (size_t)p * pstride;
+                const float l = __ldcg(q2 + 1);
+                w = l > 0.f ? expf(__ldcg(q2) - M) : 0.f;
+                L += l > 0.f ? l * w : 0.f;
+              }
+              const int cnt = min(32, a.n_splits - p0);
+#pragma unroll 4
+              for (int j = 0; j < cnt; ++j) {
+                const float wj = __shfl_sync(0xffffffffu, w, j);
+                const float2 *row = reinterpret_cast<const float2 *>(base + (size_t)(p0 + j) * pstride + 2 + EPL * lane);
+#pragma unroll
+                for (int e = 0; e < EPL / 2; ++e) {
+                  const float2 x = wj > 0.f ? __ldcg(row + e) : make_float2(0.f, 0.f);
+                  am[2 * e] += wj * x.x;
+                  am[2 * e + 1] += wj * x.y;
+                }
+              }
+            }
+            L = warp_sum(L);
+            if (a.final_to_partial) {
+              float *po = a.final_out + (size_t)hq * (size_t)(2 + P);
+              if (lane == 0) { po[0] = M; po[1] = L; }
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) po[2 + EPL * lane + e] = am[e];
+            } else {
+              const float invl = 1.f / L;
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) am[e] *= invl;
+              warp_butterflies<EPL>(am, lane);
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) {
+                const int j = EPL * lane + e;
+                if (j < dim) a.final_out[(size_t)hq * dim + j] = am[e] * isp * (((sg >> (j & 31)) & 1u) ? -1.f : 1.f);
+              }
+            }
+          }
+        }
       } else {
         const float invl = 1.f / ls;
 #pragma unroll

@@ -1045,7 +1045,7 @@ int adaptq_mha_decode_step(adaptq_mha_t h, const float *keys, const float *vals,
     return -1;
   clear_error();
   const CacheView &c = g->c;
-  constexpr int CHUNKS = 8;
+  constexpr int CHUNKS = 12; // at most; about eight are used
   const bool pinned = ptr_kind(keys) == PK_HOST_PINNED && ptr_kind(vals) == PK_HOST_PINNED &&
                       ptr_kind(queries) == PK_HOST_PINNED && ptr_kind(outs) == PK_HOST_PINNED;
   std::unique_lock<std::mutex> lk(g->mu);
@@ -1074,7 +1074,11 @@ int adaptq_mha_decode_step(adaptq_mha_t h, const float *keys, const float *vals,
   STEP_TRY(cudaEventRecord(g->ev[2 * CHUNKS], g->stream));
   STEP_TRY(cudaStreamWaitEvent(g->copy_in, g->ev[2 * CHUNKS], 0));
   const RingState before = g->u, after = advance(c, before, 1);
-  const int per = (c.n_heads + CHUNKS - 1) / CHUNKS;
+  // about an eighth of the heads per chunk, rounded down to whole waves of persistent
+  // blocks (one head per SM per round) so that no chunk ends on a partly filled wave
+  int per = (c.n_heads + 7) / 8;
+  if (per >= g->sm_count) per -= per % g->sm_count;
+  per = std::max(per, (c.n_heads + CHUNKS - 1) / CHUNKS);
   for (int ch = 0; ch < CHUNKS; ++ch) {
     const int h0 = ch * per, hc = std::min(per, c.n_heads - h0);
     if (hc <= 0) break;

@@ -46,6 +46,30 @@ FALLBACK_HBM_GBS = 6650.0
 STREAM_TRAFFIC_PER_ALG_BYTE = 1.006
 
 
+# The contract is ONE JSON line on stdout.  Libraries print there too (NCCL writes its
+# version banner to stdout when NCCL_DEBUG is set in the environment), so the process
+# keeps a private copy of the real stdout for the JSON line and points file
+# descriptor 1 at stderr for everybody else.
+_REAL_STDOUT = None
+
+
+def claim_stdout():
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    data = (json.dumps(obj) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -186,7 +210,7 @@ def run_reference(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args), "cpu_baseline": desc,
             "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit(line)
 
 
 def workload_config(args):
@@ -392,23 +416,23 @@ def run_ours(args):
     peak, peak_src = measured_peak()
     if args.mode == "append":
         if rank == 0:
-            print(json.dumps({"metric": "bulk_append_vectors_per_s", "append": append_bench(torch, L, peak)}))
+            emit({"metric": "bulk_append_vectors_per_s", "append": append_bench(torch, L, peak)})
         return
     if args.mode == "latency":
         if rank == 0:
-            print(json.dumps({"metric": "decode_latency_us_per_token", "latency": latency_bench(torch)}))
+            emit({"metric": "decode_latency_us_per_token", "latency": latency_bench(torch)})
         return
 
     if args.mode == "longctx":
         res = longctx_bench(torch, dist, world, rank, args.steps, args.warmup, peak)
         if rank == 0:
-            print(json.dumps({"metric": "long_context_decode_us_per_step", "unit": "us", "n_gpus": world,
+            emit({"metric": "long_context_decode_us_per_step", "unit": "us", "n_gpus": world,
                               "steps": args.steps, "higher_is_better": False, "scaling": "strong", "dtype": "f32",
                               "data": "synthetic",
                               "config": {"workload": "one sequence, 32 KV heads, dim 128, context 131072, KV range split "
                                                      "by token over the ranks, NCCL all-gather of split-KV partials "
                                                      "(BASELINE configs[4])", "l2": "L2 flushed before every timed step"},
-                              "results": res}))
+                              "results": res})
         if dist is not None:
             dist.barrier()
             dist.destroy_process_group()
@@ -520,7 +544,7 @@ def run_ours(args):
                 line["cpu_baseline"] = desc
             except Exception as ex:
                 line["cpu_baseline"] = {"error": repr(ex)}
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -528,6 +552,7 @@ def run_ours(args):
 
 def main():
     args = parse()
+    claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -195,14 +195,21 @@ def cpu_arm(n_heads_sample: int, context: int, steps: int, warmup: int, seqs: in
     return tok_s, desc
 
 
+def host_threads() -> int:
+    """CPU threads this process may use.  Not omp_get_max_threads(): torchrun exports
+    OMP_NUM_THREADS=1 to its children, which would make the CPU arm single-threaded at
+    N > 1 only; the timing routine sets its thread count explicitly."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import loader
-    threads = os.cpu_count() or 1
-    if loader.ref_available(fast=True):
-        threads = min(threads, loader.ref_max_threads())
+    threads = host_threads()
     n_sample = args.cpu_sample_heads or max(threads, 32)
     tok_s, desc = cpu_arm(n_sample, args.context, max(1, args.steps), args.warmup, args.seqs, threads)
     line = {"impl": "reference", "metric": "decode_attn_tokens_per_s", "value": tok_s, "unit": "tokens/s",
@@ -536,10 +543,7 @@ def run_ours(args):
                 line["append"] = {"error": repr(ex)}
         if not args.skip_cpu_baseline and world == 1:
             try:
-                threads = os.cpu_count() or 1
-                from oracle import loader
-                if loader.ref_available(fast=True):
-                    threads = min(threads, loader.ref_max_threads())
+                threads = host_threads()
                 _, desc = cpu_arm(args.cpu_sample_heads or max(threads, 32), n, 4, 1, args.seqs, threads)
                 line["cpu_baseline"] = desc
             except Exception as ex:

@@ -47,6 +47,9 @@ SYMBOLS = {
     "adaptq_mha_append_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "adaptq_mha_compute_all": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "adaptq_mha_compute_all_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "adaptq_mha_compute_partial_to_peers": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p),
+                                                       C.POINTER(C.c_void_p), C.c_int, C.c_int]),
+    "adaptq_mha_merge_from_peers": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_uint, C.c_int, C.c_void_p]),
     "adaptq_mha_decode_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
     "adaptq_mha_partial_floats": (C.c_int, [C.c_void_p]),
     "adaptq_mha_compute_partial": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),

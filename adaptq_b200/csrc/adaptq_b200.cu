@@ -652,6 +652,11 @@ void plan_spans(int n, int items_base, int sms, int &n_splits, int &span) {
 static unsigned long long *g_probe = nullptr;
 #endif
 
+// Peer destinations of the next streaming launch (set by adaptq_mha_compute_partial_to_peers
+// around its call, under the handle's mutex).
+struct PeerSpec { int n = 0, rank = 0; float *out[8] = {}; unsigned int *flag[8] = {}; };
+static thread_local const PeerSpec *tl_peers = nullptr;
+
 bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, float *partial_out) {
   const CacheView &c = g->c;
   StreamLaunch a{};
@@ -678,6 +683,11 @@ bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, flo
   a.counters = fused ? g->d_counters : nullptr;
   a.final_out = want_partial_out ? partial_out : a.out;
   a.final_to_partial = want_partial_out ? 1 : 0;
+  if (tl_peers) {
+    if (a.n_splits > 1 && !fused) { set_error("compute: too many (head, query) items for the peer exchange"); return false; }
+    a.n_peers = tl_peers->n; a.my_rank = tl_peers->rank;
+    for (int r = 0; r < tl_peers->n; ++r) { a.peer_out[r] = tl_peers->out[r]; a.peer_flag[r] = tl_peers->flag[r]; }
+  }
   const long long items = (long long)items_base * a.n_splits;
   const int grid = (int)std::min<long long>(items, g->sm_count);
   bool ok;
@@ -1118,6 +1128,80 @@ int adaptq_mha_compute_partial(adaptq_mha_t h, const float *queries, int queries
   }
   clear_error();
   return compute_all_impl(g, queries, queries_per_head, partials, true, "adaptq_mha_compute_partial");
+}
+
+// A rank whose shard is empty still has to tell its peers so: (max, sum) = (-inf, 0).
+__global__ void deliver_empty_kernel(PeerSpec ps, int items, int pf) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= items) return;
+  for (int r = 0; r < ps.n; ++r) {
+    float *po = ps.out[r] + ((size_t)ps.rank * items + i) * (size_t)pf;
+    po[0] = -INFINITY;
+    po[1] = 0.f;
+  }
+  __threadfence_system();
+  for (int r = 0; r < ps.n; ++r) atomicAdd_system(ps.flag[r] + ps.rank, 1u);
+}
+
+int adaptq_mha_compute_partial_to_peers(adaptq_mha_t h, const float *queries, int queries_per_head,
+                                        float *const *peer_bufs, unsigned int *const *peer_flags, int world, int rank) {
+  MHA_PROLOGUE("adaptq_mha_compute_partial_to_peers", -1)
+  const char *fn = "adaptq_mha_compute_partial_to_peers";
+  if (queries_per_head <= 0) { set_error("%s: queries_per_head must be positive", fn); return -1; }
+  if (!require_pointer(queries, fn, "queries") || !require_pointer(peer_bufs, fn, "peer_bufs") ||
+      !require_pointer(peer_flags, fn, "peer_flags"))
+    return -1;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) { set_error("%s: need 1 <= world <= 8 and 0 <= rank < world", fn); return -1; }
+  const CacheView &c = g->c;
+  if (c.v_mass > 0.f || c.hyb > 0 || !stream_supported(c) || g_policy.load() == 1) {
+    set_error("%s: streaming-kernel shapes only (2- or 4-bit K and V, dim 64/128, dense V, no hybrid window)", fn);
+    return -1;
+  }
+  if (ptr_kind(queries) != PK_DEVICE) { set_error("%s: queries must be device memory", fn); return -1; }
+  clear_error();
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  if (!g->uniform) { set_error("%s: heads must hold the same number of tokens", fn); return -1; }
+  PeerSpec ps;
+  ps.n = world; ps.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_bufs[r] || !peer_flags[r]) { set_error("%s: null peer pointer", fn); return -1; }
+    ps.out[r] = peer_bufs[r];
+    ps.flag[r] = peer_flags[r];
+  }
+  const int items = c.n_heads * queries_per_head;
+  if (g->u.size == 0) {
+    deliver_empty_kernel<<<(items + 127) / 128, 128, 0, g->stream>>>(ps, items, (int)partial_floats(c));
+    ++g_launches;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e)); return -1; }
+    return 0;
+  }
+  tl_peers = &ps;
+  const bool ok = compute_device(g, queries, nullptr, 0, c.n_heads, queries_per_head, g->u, true);
+  tl_peers = nullptr;
+  return ok ? g->u.size : -1;
+}
+
+int adaptq_mha_merge_from_peers(adaptq_mha_t h, const float *gather_buf, const unsigned int *flags, int world,
+                                unsigned int expected, int queries_per_head, float *outs) {
+  MHA_PROLOGUE("adaptq_mha_merge_from_peers", -1)
+  const char *fn = "adaptq_mha_merge_from_peers";
+  if (queries_per_head <= 0 || world < 1 || world > 8) { set_error("%s: bad world or queries_per_head", fn); return -1; }
+  if (!require_pointer(gather_buf, fn, "gather_buf") || !require_pointer(flags, fn, "flags") || !require_pointer(outs, fn, "outs"))
+    return -1;
+  if (ptr_kind(outs) != PK_DEVICE) { set_error("%s: outs must be device memory", fn); return -1; }
+  clear_error();
+  std::lock_guard<std::mutex> lk(g->mu);
+  DeviceGuard dg(g->device);
+  const CacheView &c = g->c;
+  const int items = c.n_heads * queries_per_head;
+  merge_peers_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
+      gather_buf, (size_t)items * partial_floats(c), world, flags, expected, g->d_status, c, 0, queries_per_head, outs);
+  ++g_launches;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e)); return -1; }
+  return 0;
 }
 
 int adaptq_mha_merge_partials(adaptq_mha_t h, const float *partials, int n_parts, int queries_per_head, float *outs) {

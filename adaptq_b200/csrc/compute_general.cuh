@@ -339,6 +339,42 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
 }
 
+// Merge of partials that PEER GPUs store into this GPU's gather buffer
+// (parts laid out [world][items][2+P]).  Rank r's kernel adds 1 to flags[r] (system
+// scope, after a system-wide fence) for every item it has delivered; `expected` is
+// the running total this step must reach.  The wait is bounded: if a peer's count
+// does not arrive within the spin budget the block records status 3, writes zeros and
+// returns, so a lost peer costs an error code, never a hang.
+__global__ void __launch_bounds__(CG_THREADS) merge_peers_kernel(
+    const float *parts, size_t part_stride, int world, const unsigned int *flags, unsigned int expected, int *status,
+    CacheView c, int head0, int nq, float *out) {
+  extern __shared__ __align__(16) unsigned char smem_gen[];
+  __shared__ int s_ok;
+  const int item = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < world && ok; ++r) {
+      unsigned int seen = 0;
+      int spins = 0;
+      for (;;) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
+        if ((int)(seen - expected) >= 0) break; // counts only grow; compare modulo 2^32
+        if (++spins > (1 << 20)) { ok = 0; break; }  // ~0.1-0.3 s
+        __nanosleep(100);
+      }
+    }
+    if (!ok) atomicExch(status, 3);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) {
+    for (int j = threadIdx.x; j < c.dim; j += CG_THREADS) out[(size_t)item * c.dim + j] = 0.f;
+    return;
+  }
+  merge_partials_block(parts, part_stride, world, c, item, head0 + item / nq, out, 0, 0,
+                       reinterpret_cast<float *>(smem_gen));
+}
+
 // ---------------------------------------------------------------------------
 // Sparse V (upstream attention/attention.cpp:448-473): the heaviest softmax
 // weights are accumulated, four at a time, until their running mass reaches

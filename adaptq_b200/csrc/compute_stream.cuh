@@ -83,6 +83,13 @@ struct StreamLaunch {
   int *counters;         // [heads_in_call*nq] arrival counts, zero before and after every launch (nullptr: no fused merge)
   float *final_out;      // outputs, or combined partials when final_to_partial
   int final_to_partial;
+  // Peer exchange (sequence sharded over GPUs): instead of final_out, the combined partial of
+  // item i goes to peer_out[r] + (my_rank*items + i)*(2+P) for every rank r (plain stores over
+  // NVLink; r == my_rank is this GPU's own buffer), followed by a system-scope add of 1 to
+  // peer_flag[r][my_rank], which the receiving rank's merge kernel waits for.
+  int n_peers, my_rank;
+  float *peer_out[8];
+  unsigned int *peer_flag[8];
 #ifdef AQ_PROBE
   unsigned long long *probe; // per-phase cycle counters (diagnostic builds only)
 #endif
@@ -411,6 +418,18 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       __syncwarp();
       if (lane == 0) mbar_arrive(&qfull[b]);
     };
+    // Combined partial of item hq -> every rank's gather buffer, then one count per rank.
+    auto deliver_to_peers = [&](int hq, float M, float L, const float (&acc)[EPL]) {
+      for (int r = 0; r < a.n_peers; ++r) {
+        float *po = a.peer_out[r] + ((size_t)a.my_rank * items_base + hq) * (size_t)(2 + P);
+        if (lane == 0) { po[0] = M; po[1] = L; }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) po[2 + EPL * lane + e] = acc[e];
+      }
+      __threadfence_system(); // the stores above are visible system-wide before the counts move
+      __syncwarp();
+      if (lane < a.n_peers) atomicAdd_system(a.peer_flag[lane] + a.my_rank, 1u);
+    };
     if (item_begin < item_end) prologue(item_begin);
     for (int item = item_begin, idx = 0; item < item_end; ++item, ++idx) {
       const uint32_t sg = sg_latest;
@@ -425,7 +444,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       const float mx = ab[P], ls = ab[P + 1];
       __syncwarp();
       if (lane == 0) mbar_arrive(&aempty[b]); // values are in registers: the slot may be refilled
-      if (a.n_splits > 1 || a.force_partial) {
+      if (a.n_peers > 0 && a.n_splits == 1) { // a single span already is the combined partial
+        deliver_to_peers(hq, mx, ls, v);
+      } else if (a.n_splits > 1 || a.force_partial) {
         float *pp = a.partial + ((size_t)split * items_base + hq) * (size_t)(2 + P);
         if (lane == 0) { pp[0] = mx; pp[1] = ls; }
 #pragma unroll
@@ -475,7 +496,9 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
               }
             }
             L = warp_sum(L);
-            if (a.final_to_partial) {
+            if (a.n_peers > 0) {
+              deliver_to_peers(hq, M, L, am);
+            } else if (a.final_to_partial) {
               float *po = a.final_out + (size_t)hq * (size_t)(2 + P);
               if (lane == 0) { po[0] = M; po[1] = L; }
 #pragma unroll

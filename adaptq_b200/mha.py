@@ -175,6 +175,29 @@ class MHAContext:
             raise RuntimeError(_lib.last_error())
         return ok
 
+    def compute_partial_to_peers(self, queries, peer_buf_ptrs, peer_flag_ptrs, rank):
+        """Split-KV partials stored straight into every rank's gather buffer (device
+        addresses as mapped in this process) -- see adaptq_mha_compute_partial_to_peers."""
+        qp, qk, _ = _as_arg(queries)
+        shape = tuple(qk.shape)
+        nq = 1 if len(shape) == 2 else shape[1]
+        world = len(peer_buf_ptrs)
+        bufs = (C.c_void_p * world)(*[int(p) for p in peer_buf_ptrs])
+        flags = (C.c_void_p * world)(*[int(p) for p in peer_flag_ptrs])
+        if self._L.adaptq_mha_compute_partial_to_peers(self._h, qp, nq, bufs, flags, world, rank) < 0:
+            raise RuntimeError(_lib.last_error())
+
+    def merge_from_peers(self, gather_buf_ptr, flags_ptr, world, expected, nq=1, out=None):
+        """Wait for every rank's arrival count to reach `expected`, merge, write [n_heads, nq, dim]."""
+        if out is None:
+            out = torch.empty((self._n_heads, nq, self._head_dim), dtype=torch.float32, device="cuda")
+        op, ok, _ = _as_arg(out)
+        rc = self._L.adaptq_mha_merge_from_peers(self._h, C.c_void_p(int(gather_buf_ptr)), C.c_void_p(int(flags_ptr)), world,
+                                                 C.c_uint(expected & 0xFFFFFFFF), nq, op)
+        if rc < 0:
+            raise RuntimeError(_lib.last_error())
+        return ok
+
     def merge_partials(self, partials, nq=1, out=None):
         """partials: [n_parts, n_heads, nq, 2+padded] -> [n_heads, nq, dim]."""
         pp, pk, _ = _as_arg(partials)

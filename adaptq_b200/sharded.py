@@ -34,6 +34,39 @@ def local_token_slice(first_token: int, n_tokens: int, world: int, rank: int) ->
     return slice(start, n_tokens, world)
 
 
+class PeerGather:
+    """Gather buffers that every rank can store into directly (torch symmetric
+    memory over NVLink), for ShardedSequence(..., exchange="peer"): per rank two
+    buffers [world][items][partial_floats] used in turn, and `world` arrival
+    counts that only ever grow.  The streaming kernel of rank r stores each
+    head's combined partial into slice [r] of every rank's buffer and bumps
+    that rank's count; the merge kernel waits for the counts (bounded) -- no
+    collective call on the data path."""
+
+    def __init__(self, items: int, partial_floats: int, world: int, rank: int, group=None):
+        import torch
+        import torch.distributed as dist
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only, no multicast binding
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.items, self.world, self.rank = items, world, rank
+        n_buf = world * items * partial_floats
+        self._t = symm.empty(2 * n_buf + 64, dtype=torch.float32, device="cuda")
+        self._t.zero_()
+        try:
+            symm.enable_symm_mem_for_group(group.group_name)
+        except Exception:
+            pass  # newer torch enables every group
+        hdl = symm.rendezvous(self._t, group)
+        base = [int(p) for p in hdl.buffer_ptrs]
+        self.buf_ptrs = [[b + 4 * par * n_buf for b in base] for par in (0, 1)]
+        self.flag_ptrs = [b + 8 * n_buf for b in base]
+        torch.cuda.synchronize()
+        dist.barrier(group)  # every rank's counts are zero before anybody delivers
+        self.step = 0
+
+
 class ShardedSequence:
     """One logical KV cache of `capacity` tokens per head, spread over the ranks
     of `group` by token.  `make_context(local_capacity)` must return an object
@@ -41,13 +74,17 @@ class ShardedSequence:
     on a GPU; tests substitute a CPU stand-in).  `all_gather(tensor) -> stacked
     tensor [world, ...]` defaults to torch.distributed.all_gather_into_tensor."""
 
-    def __init__(self, make_context, capacity: int, world: int, rank: int, all_gather=None):
+    def __init__(self, make_context, capacity: int, world: int, rank: int, all_gather=None, exchange: str = "nccl"):
         if capacity % world != 0:
             raise ValueError("capacity must be a multiple of the number of ranks to keep FIFO eviction exact")
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
         self.world, self.rank = world, rank
         self.ctx = make_context(capacity // world)
         self.pos = 0
         self._gather = all_gather or self._dist_all_gather
+        self._exchange = exchange
+        self._peer = None  # PeerGather, made on the first compute (it needs the query count)
 
     @staticmethod
     def _dist_all_gather(t):
@@ -70,6 +107,17 @@ class ShardedSequence:
     def compute(self, queries):
         """queries: [heads, dim] or [heads, nq, dim], the same on every rank -> outputs on every rank."""
         nq = 1 if len(queries.shape) == 2 else queries.shape[1]
+        if self._exchange == "peer":
+            if self._peer is None or self._peer.items != self.ctx.n_heads * nq:
+                pf = self.ctx._L.adaptq_mha_partial_floats(self.ctx._h)
+                self._peer = PeerGather(self.ctx.n_heads * nq, pf, self.world, self.rank)
+            pg = self._peer
+            par = pg.step & 1
+            self.ctx.compute_partial_to_peers(queries, pg.buf_ptrs[par], pg.flag_ptrs, self.rank)
+            pg.step += 1
+            out = self.ctx.merge_from_peers(pg.buf_ptrs[par][self.rank], pg.flag_ptrs[self.rank], self.world,
+                                            pg.step * pg.items, nq)
+            return out[:, 0] if len(queries.shape) == 2 else out
         part = self.ctx.compute_partial(queries)     # [heads, nq, 2+padded]
         parts = self._gather(part)                   # [world, heads, nq, 2+padded]
         out = self.ctx.merge_partials(parts, nq=nq)  # [heads, nq, dim]

@@ -82,6 +82,9 @@ def parse():
                     help="append: only the bulk-append kernel benchmark; latency: per-token decode latency of the "
                          "small per-layer configurations (BASELINE configs[0..2]); longctx: one 131072-token "
                          "sequence with its KV range split over the ranks (BASELINE configs[4])")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="longctx mode: combine the ranks' partials with an NCCL all-gather, or let the kernels store "
+                         "them into every rank's buffer over NVLink (torch symmetric memory)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-append-bench", action="store_true")
     ap.add_argument("--cpu-sample-heads", type=int, default=0)
@@ -324,7 +327,7 @@ def latency_bench(torch):
     return out
 
 
-def longctx_bench(torch, dist, world, rank, steps, warmup, peak):
+def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"):
     """BASELINE configs[4]: ONE sequence, 1 layer, 32 KV heads, dim 128, context
     131072, K2/V2 and K4/V4, K/V Student-t(nu=3), dense V.  Token t lives on rank
     t mod G (local ring of 131072/G tokens).  One step = one decode query per
@@ -357,7 +360,18 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak):
         part = torch.empty((H, 1, 2 + D), device="cuda")
         parts = torch.empty((world, H, 1, 2 + D), device="cuda")
 
+        pg = None
+        if exchange == "peer" and dist is not None:
+            from adaptq_b200.sharded import PeerGather
+            pg = PeerGather(H, 2 + D, world, rank)
+
         def step_sharded():
+            if pg is not None:  # the kernels deliver to every rank's buffer; the merge waits on arrival counts
+                par = pg.step & 1
+                ctx.compute_partial_to_peers(q, pg.buf_ptrs[par], pg.flag_ptrs, rank)
+                pg.step += 1
+                ctx.merge_from_peers(pg.buf_ptrs[par][rank], pg.flag_ptrs[rank], world, pg.step * pg.items, 1, out=o)
+                return
             ctx.compute_partial(q, out=part)
             if dist is not None:
                 dist.all_gather_into_tensor(parts, part)
@@ -431,14 +445,16 @@ def run_ours(args):
         return
 
     if args.mode == "longctx":
-        res = longctx_bench(torch, dist, world, rank, args.steps, args.warmup, peak)
+        res = longctx_bench(torch, dist, world, rank, args.steps, args.warmup, peak, args.exchange)
         if rank == 0:
             emit({"metric": "long_context_decode_us_per_step", "unit": "us", "n_gpus": world,
                               "steps": args.steps, "higher_is_better": False, "scaling": "strong", "dtype": "f32",
                               "data": "synthetic",
                               "config": {"workload": "one sequence, 32 KV heads, dim 128, context 131072, KV range split "
-                                                     "by token over the ranks, NCCL all-gather of split-KV partials "
-                                                     "(BASELINE configs[4])", "l2": "L2 flushed before every timed step"},
+                                                     "by token over the ranks, split-KV partials combined by "
+                                                     + ("an NCCL all-gather" if args.exchange == "nccl" else
+                                                        "kernel stores into peer memory over NVLink")
+                                                     + " (BASELINE configs[4])", "l2": "L2 flushed before every timed step"},
                               "results": res})
         if dist is not None:
             dist.barrier()

@@ -77,6 +77,38 @@ int adaptq_mha_compute_partial(adaptq_mha_t mha, const float *queries,
 int adaptq_mha_merge_partials(adaptq_mha_t mha, const float *partials,
                               int n_parts, int queries_per_head, float *outs);
 
+/* The same exchange without a collective-library call, for GPUs that can map
+ * each other's memory (NVLink peers, e.g. torch symmetric memory or CUDA IPC):
+ * the streaming kernel itself stores each head's combined partial into EVERY
+ * rank's gather buffer as soon as that head is done, so the transfer overlaps
+ * the rest of the kernel, and the receiving side's merge kernel waits on
+ * per-rank arrival counts.
+ *   peer_bufs[r]  : rank r's gather buffer, float [world][n_heads*queries_per_head]
+ *                   [adaptq_mha_partial_floats()], as mapped in THIS process;
+ *                   this rank fills slice [rank] of every buffer.
+ *   peer_flags[r] : rank r's unsigned[world] arrival counts (zero before the
+ *                   first step, never reset); this rank adds 1 to
+ *                   peer_flags[r][rank] per (head, query) delivered, at system
+ *                   scope after a system-wide fence.
+ * adaptq_mha_merge_from_peers(mha, own gather buffer, own counts, world,
+ * expected, ...) waits until every count has reached `expected` (the running
+ * total: step number x n_heads x queries_per_head, compared modulo 2^32),
+ * merges and writes outs [n_heads][queries_per_head][dim].  The wait is
+ * bounded (about a quarter of a second): if a peer never delivers, the outputs
+ * are zeros and adaptq_mha_synchronize() reports the failure.  Use two gather
+ * buffers in turn (step parity): a rank's next step may deliver while a slower
+ * peer still merges the previous one.  Streaming-kernel shapes only, device
+ * pointers only, at most 8 ranks.  No counterpart upstream. */
+int adaptq_mha_compute_partial_to_peers(adaptq_mha_t mha, const float *queries,
+                                        int queries_per_head,
+                                        float *const *peer_bufs,
+                                        unsigned int *const *peer_flags,
+                                        int world, int rank);
+int adaptq_mha_merge_from_peers(adaptq_mha_t mha, const float *gather_buf,
+                                const unsigned int *flags, int world,
+                                unsigned int expected, int queries_per_head,
+                                float *outs);
+
 /* Decode attention for every head WITHOUT any device or host allocation.
  * This entry point has no counterpart in upstream; it exists for callers
  * that must not reach the CUDA allocator after start-up -- an inference

@@ -199,3 +199,45 @@ def test_sequence_sharding_partials(gpu_lib, orc):
     parts = np.stack([s.compute_partial(q) for s in shards])
     out = shards[0].merge_partials(parts, nq=1)[:, 0]
     assert_close(out, cpu.compute(q), "merged partials")
+
+
+@pytest.mark.parametrize("T,empty_rank", [(3000, False), (40000, False), (2, True)])
+def test_peer_exchange_entry_points_on_one_device(gpu_lib, orc, T, empty_rank):
+    """adaptq_mha_compute_partial_to_peers / adaptq_mha_merge_from_peers with all "ranks"
+    on one GPU: every shard's kernel stores its partials into every rank's gather buffer
+    and bumps the arrival counts; the merges run afterwards on the same stream, so no
+    kernel ever waits for one that has not run.  Two steps, alternating buffers, counts
+    never reset.  T = 40000 makes each shard several spans long (in-kernel merge before
+    the delivery); T = 2 leaves rank 2 of 3 without tokens."""
+    import torch
+    from adaptq_b200 import MHAContext
+    from oracle import loader
+    heads, dim, G = 3, 128, 3
+    rng = np.random.default_rng(5)
+    k, v = make_kv(rng, T, heads, dim, "normal")
+    cpu = CpuHeads(orc, heads, dim, 4, 2, T, 77)
+    cpu.append_many(k, v)
+    seeds = [loader.mha_head_seed(77, h) for h in range(heads)]
+    shards = [MHAContext(heads, dim, 4, 2, T // G + 1, seeds=seeds, v_mass=0.0, hybrid_thresh=0) for _ in range(G)]
+    for r, s in enumerate(shards):
+        if len(k[r::G]):
+            s.append_all(np.ascontiguousarray(k[r::G]), np.ascontiguousarray(v[r::G]))
+    assert empty_rank == (len(k[G - 1::G]) == 0)
+    pf = gpu_lib.adaptq_mha_partial_floats(shards[0]._h)
+    n_buf = G * heads * pf
+    bufs = [torch.zeros(2 * n_buf, device="cuda") for _ in range(G)]
+    flags = [torch.zeros(G, dtype=torch.int32, device="cuda") for _ in range(G)]
+    for step in range(2):
+        q = rng.standard_normal((heads, dim)).astype(np.float32)
+        qd = torch.from_numpy(q).cuda()
+        par = step & 1
+        buf_ptrs = [b.data_ptr() + 4 * par * n_buf for b in bufs]
+        flag_ptrs = [f.data_ptr() for f in flags]
+        for r, s in enumerate(shards):
+            s.compute_partial_to_peers(qd, buf_ptrs, flag_ptrs, r)
+        want = cpu.compute(q)
+        for r, s in enumerate(shards):
+            out = s.merge_from_peers(buf_ptrs[r], flag_ptrs[r], G, (step + 1) * heads)
+            s.synchronize()
+            assert_close(out[:, 0].cpu().numpy(), want, f"step {step} rank {r}")
+    assert all(int(x) == 2 * heads for f in flags for x in f.cpu())

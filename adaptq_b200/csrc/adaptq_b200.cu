@@ -1196,8 +1196,8 @@ int adaptq_mha_merge_from_peers(adaptq_mha_t h, const float *gather_buf, const u
   DeviceGuard dg(g->device);
   const CacheView &c = g->c;
   const int items = c.n_heads * queries_per_head;
-  merge_peers_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
-      gather_buf, (size_t)items * partial_floats(c), world, flags, expected, g->d_status, c, 0, queries_per_head, outs);
+  merge_peers_kernel<<<(items + 3) / 4, 128, 4 * c.padded * sizeof(float), g->stream>>>(
+      gather_buf, (size_t)items * partial_floats(c), world, flags, expected, g->d_status, c, 0, queries_per_head, items, outs);
   ++g_launches;
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e)); return -1; }

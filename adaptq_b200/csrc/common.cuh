@@ -144,6 +144,33 @@ __device__ __forceinline__ void block_butterflies(float *x, int p) {
   }
 }
 
+// Walsh-Hadamard butterflies over P = 32*EPL values held EPL per lane (lane l
+// owns elements EPL*l .. EPL*l+EPL-1), stage order len = 1, 2, ... P/2, lower
+// index a+b, upper a-b (core/fwht.cpp:36-57).  One warp, no shared memory.
+template <int EPL> __device__ __forceinline__ void warp_butterflies(float (&v)[EPL], int lane) {
+#pragma unroll
+  for (int len = 1; len < EPL; len <<= 1) {
+#pragma unroll
+    for (int i = 0; i < EPL; i += (len << 1)) {
+#pragma unroll
+      for (int j = 0; j < len; ++j) {
+        const float a = v[i + j], b = v[i + j + len];
+        v[i + j] = a + b;
+        v[i + j + len] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
+      v[e] = upper ? other - v[e] : v[e] + other;
+    }
+  }
+}
+
 __device__ __forceinline__ float sign_of(const uint32_t *signs, int i) {
   return ((signs[i >> 5] >> (i & 31)) & 1u) ? -1.0f : 1.0f;
 }

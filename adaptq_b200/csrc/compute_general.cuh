@@ -339,40 +339,98 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
 }
 
+template <int EPL>
+__device__ __forceinline__ void peers_finish(const float *base, size_t part_stride, int world, float w_p, float invL, float isp,
+                                             const uint32_t *sg, int dim, int lane, float *o) {
+  float v[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) v[e] = 0.f;
+  for (int r = 0; r < world; ++r) {
+    const float w = __shfl_sync(0xffffffffu, w_p, r);
+    if (w > 0.f) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[e] += w * __ldcg(base + (size_t)r * part_stride + 2 + EPL * lane + e);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) v[e] *= invL;
+  warp_butterflies<EPL>(v, lane);
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const int j = EPL * lane + e;
+    if (j < dim) o[j] = v[e] * isp * sign_of(sg, j);
+  }
+}
+
 // Merge of partials that PEER GPUs store into this GPU's gather buffer
 // (parts laid out [world][items][2+P]).  Rank r's kernel adds 1 to flags[r] (system
 // scope, after a system-wide fence) for every item it has delivered; `expected` is
 // the running total this step must reach.  The wait is bounded: if a peer's count
 // does not arrive within the spin budget the block records status 3, writes zeros and
 // returns, so a lost peer costs an error code, never a hang.
-__global__ void __launch_bounds__(CG_THREADS) merge_peers_kernel(
+__global__ void __launch_bounds__(128) merge_peers_kernel(
     const float *parts, size_t part_stride, int world, const unsigned int *flags, unsigned int expected, int *status,
-    CacheView c, int head0, int nq, float *out) {
-  extern __shared__ __align__(16) unsigned char smem_gen[];
-  __shared__ int s_ok;
-  const int item = blockIdx.x;
-  if (threadIdx.x == 0) {
-    int ok = 1;
-    for (int r = 0; r < world && ok; ++r) {
-      unsigned int seen = 0;
-      int spins = 0;
-      for (;;) {
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
-        if ((int)(seen - expected) >= 0) break; // counts only grow; compare modulo 2^32
-        if (++spins > (1 << 20)) { ok = 0; break; }  // ~0.1-0.3 s
-        __nanosleep(100);
-      }
+    CacheView c, int head0, int nq, int items, float *out) {
+  // one warp per (head, query): at most 8 partials of at most 1024 floats, no block barriers
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int P = c.padded, dim = c.dim;
+  int ok = 1;
+  if (lane < world) {
+    unsigned int seen = 0;
+    int spins = 0;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + lane) : "memory");
+      if ((int)(seen - expected) >= 0) break;       // counts only grow; compare modulo 2^32
+      if (++spins > (1 << 20)) { ok = 0; break; }   // about a quarter of a second
+      __nanosleep(100);
     }
-    if (!ok) atomicExch(status, 3);
-    s_ok = ok;
   }
-  __syncthreads();
-  if (!s_ok) {
-    for (int j = threadIdx.x; j < c.dim; j += CG_THREADS) out[(size_t)item * c.dim + j] = 0.f;
+  ok = __all_sync(0xffffffffu, ok);
+  float *o = out + (size_t)item * dim;
+  if (!ok) {
+    if (lane == 0) atomicExch(status, 3);
+    for (int j = lane; j < dim; j += 32) o[j] = 0.f;
     return;
   }
-  merge_partials_block(parts, part_stride, world, c, item, head0 + item / nq, out, 0, 0,
-                       reinterpret_cast<float *>(smem_gen));
+  const float *base = parts + (size_t)item * (2 + P);
+  float m_p = -INFINITY, l_p = 0.f;
+  if (lane < world) {
+    l_p = __ldcg(base + (size_t)lane * part_stride + 1);
+    if (l_p > 0.f) m_p = __ldcg(base + (size_t)lane * part_stride);
+  }
+  const float M = warp_max(m_p);
+  const float w_p = l_p > 0.f ? expf(m_p - M) : 0.f;
+  const float L = warp_sum(l_p > 0.f ? l_p * w_p : 0.f);
+  const float invL = 1.f / L;
+  const uint32_t *sg = c.signs + (size_t)(head0 + item / nq) * c.sign_words;
+  const float isp = 1.f / sqrtf((float)P);
+  // the usual sizes: in registers, butterflies with shuffles (lane l owns elements EPL*l .. EPL*l+EPL-1)
+  if (P == 128) { peers_finish<4>(base, part_stride, world, w_p, invL, isp, sg, dim, lane, o); return; }
+  if (P == 64) { peers_finish<2>(base, part_stride, world, w_p, invL, isp, sg, dim, lane, o); return; }
+  // other padded sizes: through this warp's slice of shared memory
+  extern __shared__ __align__(16) unsigned char smem_gen[];
+  float *vec = reinterpret_cast<float *>(smem_gen) + (size_t)(threadIdx.x >> 5) * P;
+  for (int j = lane; j < P; j += 32) {
+    float sacc = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const float w = __shfl_sync(0xffffffffu, w_p, r);
+      if (w > 0.f) sacc += w * __ldcg(base + (size_t)r * part_stride + 2 + j);
+    }
+    vec[j] = sacc * invL;
+  }
+  __syncwarp();
+  for (int len = 1; len < P; len <<= 1) {
+    for (int t = lane; t < (P >> 1); t += 32) {
+      const int i = ((t / len) * (len << 1)) + (t % len);
+      const float x = vec[i], y = vec[i + len];
+      vec[i] = x + y;
+      vec[i + len] = x - y;
+    }
+    __syncwarp();
+  }
+  for (int j = lane; j < dim; j += 32) o[j] = vec[j] * isp * sign_of(sg, j);
 }
 
 // ---------------------------------------------------------------------------

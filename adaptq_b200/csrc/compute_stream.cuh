@@ -151,33 +151,6 @@ __device__ __forceinline__ void consumer_sum2(float &a, float &b, float *red) {
   }
 }
 
-// Walsh-Hadamard butterflies over P = 32*EPL values held EPL per lane (lane l
-// owns elements EPL*l .. EPL*l+EPL-1), stage order len = 1, 2, ... P/2, lower
-// index a+b, upper a-b (core/fwht.cpp:36-57).  One warp, no shared memory.
-template <int EPL> __device__ __forceinline__ void warp_butterflies(float (&v)[EPL], int lane) {
-#pragma unroll
-  for (int len = 1; len < EPL; len <<= 1) {
-#pragma unroll
-    for (int i = 0; i < EPL; i += (len << 1)) {
-#pragma unroll
-      for (int j = 0; j < len; ++j) {
-        const float a = v[i + j], b = v[i + j + len];
-        v[i + j] = a + b;
-        v[i + j + len] = a - b;
-      }
-    }
-  }
-#pragma unroll
-  for (int m = 1; m < 32; m <<= 1) {
-    const bool upper = (lane & m) != 0;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
-      v[e] = upper ? other - v[e] : v[e] + other;
-    }
-  }
-}
-
 // Sum STEPS per-lane partials across the 8 lanes of a token group so that
 // each lane ends with complete sums; returns the value this lane owns and the
 // step it belongs to (8 steps: lane wl owns step wl; 4 steps: lanes wl, wl^1
@@ -426,9 +399,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
         for (int e = 0; e < EPL; ++e) po[2 + EPL * lane + e] = acc[e];
       }
-      __threadfence_system(); // the stores above are visible system-wide before the counts move
+      // The counts move with release semantics at system scope: the warp barrier orders every
+      // lane's stores before the releasing lanes, and a release is cumulative, so whoever
+      // acquires the new count also sees the partial.
       __syncwarp();
-      if (lane < a.n_peers) atomicAdd_system(a.peer_flag[lane] + a.my_rank, 1u);
+      if (lane < a.n_peers)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.peer_flag[lane] + a.my_rank) : "memory");
     };
     if (item_begin < item_end) prologue(item_begin);
     for (int item = item_begin, idx = 0; item < item_end; ++item, ++idx) {

@@ -82,7 +82,7 @@ def parse():
                     help="append: only the bulk-append kernel benchmark; latency: per-token decode latency of the "
                          "small per-layer configurations (BASELINE configs[0..2]); longctx: one 131072-token "
                          "sequence with its KV range split over the ranks (BASELINE configs[4])")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="longctx mode: combine the ranks' partials with an NCCL all-gather, or let the kernels store "
                          "them into every rank's buffer over NVLink (torch symmetric memory)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
@@ -388,7 +388,7 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
         def timed(fn):
             for _ in range(max(3, warmup)):
                 fn()
-            tot = 0.0
+            samples = []
             for _ in range(steps):
                 flush.fill_(1)
                 torch.cuda.synchronize()
@@ -400,8 +400,9 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
                 fn()
                 b.record()
                 torch.cuda.synchronize()
-                tot += a.elapsed_time(b)
-            t = torch.tensor([tot / steps], device="cuda")
+                samples.append(a.elapsed_time(b))
+            samples.sort()  # the median: a step that catches a stray millisecond must not carry the figure
+            t = torch.tensor([samples[len(samples) // 2]], device="cuda")
             if dist is not None:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t.item()) * 1e3  # us

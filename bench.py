@@ -3,7 +3,7 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Workload (BASELINE.json configs[3], the configuration the metric is quoted on):
+Workload (configuration 4 of the benchmark contract, the one the metric is quoted on):
 batched decode at Llama-3-8B KV shape -- 256 independent sequences x 32 layers
 x 8 KV heads = 65 536 head-instances per GPU, head dim 128, context 8192,
 K 4-bit / V 2-bit, dense V, no hybrid window.  K/V are N(0,1) with 1 % of the
@@ -76,12 +76,12 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--seqs", type=int, default=SEQS, help="sequences per GPU (default: the BASELINE config)")
+    ap.add_argument("--seqs", type=int, default=SEQS, help="sequences per GPU (default: the contract's 256)")
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--mode", default="decode", choices=["decode", "append", "latency", "longctx"],
                     help="append: only the bulk-append kernel benchmark; latency: per-token decode latency of the "
-                         "small per-layer configurations (BASELINE configs[0..2]); longctx: one 131072-token "
-                         "sequence with its KV range split over the ranks (BASELINE configs[4])")
+                         "small per-layer configurations (contract configurations 1-3); longctx: one 131072-token "
+                         "sequence with its KV range split over the ranks (contract configuration 5)")
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="longctx mode: combine the ranks' partials with an NCCL all-gather, or let the kernels store "
                          "them into every rank's buffer over NVLink (torch symmetric memory)")
@@ -250,7 +250,7 @@ def fill_cache(ctx, heads, context, torch, gen):
 
 
 def append_bench(torch, L, peak):
-    """BASELINE configs[3] bulk append: 32768 tokens x 8 heads x 128, K and V, bits 2/3/4."""
+    """The contract's bulk append: 32768 tokens x 8 heads x 128, K and V, bits 2/3/4."""
     import adaptq_b200
     out = {}
     T, H = 32768, 8
@@ -328,7 +328,7 @@ def latency_bench(torch):
 
 
 def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"):
-    """BASELINE configs[4]: ONE sequence, 1 layer, 32 KV heads, dim 128, context
+    """Contract configuration 5: ONE sequence, 1 layer, 32 KV heads, dim 128, context
     131072, K2/V2 and K4/V4, K/V Student-t(nu=3), dense V.  Token t lives on rank
     t mod G (local ring of 131072/G tokens).  One step = one decode query per
     head: every rank runs the split-KV kernel over its shard, the (max, sum,

@@ -1,8 +1,8 @@
 #!/usr/bin/env bash
 # build_ref.sh -- TEST INFRASTRUCTURE.
 #
-# Compiles the UPSTREAM AdapTQ hot-path sources where they lie (default
-# /root/reference, override with ADAPTQ_REFERENCE_DIR) into oracle/_ref/:
+# Compiles the UPSTREAM AdapTQ hot-path sources where they lie (the checkout
+# named by ADAPTQ_REFERENCE_DIR, else the default below) into oracle/_ref/:
 #
 #   libadaptq_ref.so       -O3 -ffp-contract=off   parity build (bit-exact indices)
 #   libadaptq_ref_fast.so  -O3 -mavx2 -mfma        timed CPU baseline build

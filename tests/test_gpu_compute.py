@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 # dim, k_bits, v_bits, capacity, tokens, v_mass, hybrid, dist
 CASES = [
-    (64, 4, 2, 2048, 2048, 0.0, 0, "normal"),                    # BASELINE config 1, dense V
+    (64, 4, 2, 2048, 2048, 0.0, 0, "normal"),                    # the reference's own CPU-runnable configuration, dense V
     (64, 4, 2, 1152, 1100, 0.0, 0, "student4_outlier"),          # config 2 shape, heavy tails
     (64, 4, 2, 1024, 1100, 0.0, 0, "student4_outlier"),          # wrapped ring
     (64, 16, 2, 1152, 1100, 0.0, 0, "student4_outlier"),         # layer-0 K passthrough
@@ -68,7 +68,7 @@ def sparse_cut(weights, v_mass):
                                             # 4096- and 8192-token block sorts, and the device-wide sort beyond
                                             (128, 4, 2, 3000, 0.9), (64, 2, 2, 6000, 0.95), (64, 4, 2, 9000, 0.9)])
 def test_sparse_v_matches_oracle(gpu_lib, orc, dim, kb, vb, T, vm):
-    """Engine defaults past the hybrid window (BASELINE config 1 'as-is').  The cut
+    """Engine defaults past the hybrid window (the reference's own CPU-runnable configuration as it ships).  The cut
     is found in blocks of four rows, so a query whose running mass lands within
     rounding distance of v_mass may legitimately stop one block earlier or later;
     such borderline queries are skipped, every other one must match."""

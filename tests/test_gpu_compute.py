@@ -241,3 +241,31 @@ def test_peer_exchange_entry_points_on_one_device(gpu_lib, orc, T, empty_rank):
             s.synchronize()
             assert_close(out[:, 0].cpu().numpy(), want, f"step {step} rank {r}")
     assert all(int(x) == 2 * heads for f in flags for x in f.cpu())
+
+
+def test_peer_merge_gives_up_when_a_rank_never_delivers(gpu_lib, orc):
+    """Failure detection without a fault: of two "ranks" only rank 0 delivers, so the
+    arrival count of rank 1 never moves.  The merge kernel's wait runs out by itself
+    (about a second), the outputs are zeros, adaptq_mha_synchronize() reports the
+    failure, and the handle keeps working afterwards."""
+    import torch
+    from adaptq_b200 import MHAContext
+    heads, dim, T = 2, 128, 300
+    rng = np.random.default_rng(9)
+    k, v = make_kv(rng, T, heads, dim, "normal")
+    ctx = MHAContext(heads, dim, 4, 2, T, seed=3, v_mass=0.0, hybrid_thresh=0)
+    ctx.append_all(k, v)
+    pf = gpu_lib.adaptq_mha_partial_floats(ctx._h)
+    bufs = [torch.zeros(2 * heads * pf, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    q = torch.from_numpy(rng.standard_normal((heads, dim)).astype(np.float32)).cuda()
+    ctx.compute_partial_to_peers(q, [b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], 0)
+    out = ctx.merge_from_peers(bufs[0].data_ptr(), flags[0].data_ptr(), 2, heads)  # rank 1's count stays 0
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        ctx.synchronize()
+    assert float(out.abs().max()) == 0.0
+    # the context is intact: a normal call still answers, and matches the oracle
+    cpu = CpuHeads(orc, heads, dim, 4, 2, T, 3)
+    cpu.append_many(k, v)
+    assert_close(ctx.compute_all(q).cpu().numpy(), cpu.compute(q.cpu().numpy()), "after the timed-out merge")
+    ctx.synchronize()

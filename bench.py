@@ -363,7 +363,15 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
         pg = None
         if exchange == "peer" and dist is not None:
             from adaptq_b200.sharded import PeerGather
-            pg = PeerGather(H, 2 + D, world, rank)
+            ok = torch.ones(1, device="cuda")
+            try:
+                pg = PeerGather(H, 2 + D, world, rank)
+            except Exception as ex:  # no mappable peer memory on this box: every rank falls back together
+                print(f"peer exchange unavailable ({ex!r}); using the NCCL all-gather", file=sys.stderr)
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if float(ok.item()) == 0.0:
+                pg = None
 
         def step_sharded():
             if pg is not None:  # the kernels deliver to every rank's buffer; the merge waits on arrival counts
@@ -410,7 +418,7 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
         alg = H * (N * (D * kb // 8 + D * vb // 8 + 8) + 8 * D)
         us_total = timed(step_sharded)
         us_local = timed(step_local)
-        res = {"us_per_step": us_total, "us_local_kernels": us_local, "us_gather_and_merge": us_total - us_local,
+        res = {"exchange": "none" if dist is None else ("peer" if pg is not None else "nccl"), "us_per_step": us_total, "us_local_kernels": us_local, "us_gather_and_merge": us_total - us_local,
                "effective_kv_gbs_all_ranks": alg / us_total / 1e3, "local_kernel_gbs_per_gpu": alg / world / us_local / 1e3,
                "local_kernel_frac_of_peak": alg / world / us_local / 1e3 / peak,
                "algorithmic_bytes": alg, "tokens_per_rank": local_n}

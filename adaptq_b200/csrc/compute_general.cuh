@@ -339,6 +339,8 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
 }
 
+// Tail of merge_peers_kernel for P = 32*EPL: weighted sum of the ranks' accumulators,
+// normalisation, inverse transform (core/fwht.cpp:106-134) and store, all in one warp.
 template <int EPL>
 __device__ __forceinline__ void peers_finish(const float *base, size_t part_stride, int world, float w_p, float invL, float isp,
                                              const uint32_t *sg, int dim, int lane, float *o) {
@@ -364,9 +366,9 @@ __device__ __forceinline__ void peers_finish(const float *base, size_t part_stri
 
 // Merge of partials that PEER GPUs store into this GPU's gather buffer
 // (parts laid out [world][items][2+P]).  Rank r's kernel adds 1 to flags[r] (system
-// scope, after a system-wide fence) for every item it has delivered; `expected` is
-// the running total this step must reach.  The wait is bounded: if a peer's count
-// does not arrive within the spin budget the block records status 3, writes zeros and
+// scope, with release semantics) for every item it has delivered; `expected` is the
+// running total this step must reach.  The wait is bounded: if a peer's count does
+// not arrive within the spin budget the warp records status 3, writes zeros and
 // returns, so a lost peer costs an error code, never a hang.
 __global__ void __launch_bounds__(128) merge_peers_kernel(
     const float *parts, size_t part_stride, int world, const unsigned int *flags, unsigned int expected, int *status,

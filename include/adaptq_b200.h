@@ -88,8 +88,8 @@ int adaptq_mha_merge_partials(adaptq_mha_t mha, const float *partials,
  *                   this rank fills slice [rank] of every buffer.
  *   peer_flags[r] : rank r's unsigned[world] arrival counts (zero before the
  *                   first step, never reset); this rank adds 1 to
- *                   peer_flags[r][rank] per (head, query) delivered, at system
- *                   scope after a system-wide fence.
+ *                   peer_flags[r][rank] per (head, query) delivered, with
+ *                   release semantics at system scope.
  * adaptq_mha_merge_from_peers(mha, own gather buffer, own counts, world,
  * expected, ...) waits until every count has reached `expected` (the running
  * total: step number x n_heads x queries_per_head, compared modulo 2^32),

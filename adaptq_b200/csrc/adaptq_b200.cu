@@ -131,7 +131,10 @@ __global__ void segment_offsets_kernel(int *begin, int *end, int n_seg, int stri
 void free_group(Group *g) {
   if (!g) return;
   DeviceGuard dg(g->device);
-  if (g->stream == nullptr || true) cudaDeviceSynchronize();
+  // wait for this handle's own work only (the legacy stream when no stream was set)
+  cudaStreamSynchronize(g->stream);
+  if (g->copy_in) cudaStreamSynchronize(g->copy_in);
+  if (g->copy_out) cudaStreamSynchronize(g->copy_out);
   cudaFree(g->c.k_slab); cudaFree(g->c.v_slab); cudaFree(g->c.k_scale); cudaFree(g->c.v_scale);
   cudaFree((void *)g->c.signs); cudaFree(g->c.mirror);
   cudaFree(g->d_stage); cudaFree(g->d_scratch_base); cudaFree(g->d_status);
@@ -315,18 +318,31 @@ bool check_status(Group *g, const char *fn) {
   return true;
 }
 
+// Dynamic shared-memory limit of a kernel, raised once per device (and again only
+// when a larger size is asked for).  `slot` is the caller's per-kernel table; calls
+// hold different handles' mutexes, so the table has its own lock.
+constexpr int MAX_DEVICES = 64;
+std::mutex g_attr_mu;
+template <typename K>
+bool ensure_smem_limit(K kern, int (&slot)[MAX_DEVICES], int device, size_t bytes, const char *what) {
+  std::lock_guard<std::mutex> lk(g_attr_mu);
+  if (device < 0 || device >= MAX_DEVICES) { set_error("%s: device ordinal %d is not supported (0..%d)", what, device, MAX_DEVICES - 1); return false; }
+  if ((int)bytes > slot[device]) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), what);
+    slot[device] = (int)bytes;
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------------------
 // append
 // ---------------------------------------------------------------------------
 template <int P, int BITS>
 bool launch_rows(Group *g, const AppendLaunch &a) {
   constexpr size_t SMEM = ((size_t)AT_TILE * (P + 4) + (size_t)(AT_THREADS / 32) * P) * sizeof(float);
-  static bool configured[64] = {};
+  static int configured[MAX_DEVICES] = {};
   auto kern = append_tile_kernel<P, BITS>;
-  if (!configured[g->device & 63]) {
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM), "append");
-    configured[g->device & 63] = true;
-  }
+  if (!ensure_smem_limit(kern, configured, g->device, SMEM, "append")) return false;
   long long items = (long long)a.heads_in_call * a.n_tokens;
   long long tiles = (items + AT_TILE - 1) / AT_TILE;
   int grid = (int)std::min<long long>(tiles, (long long)g->sm_count * AT_BLOCKS_PER_SM);
@@ -350,12 +366,9 @@ bool launch_rows_bits(Group *g, const AppendLaunch &a, int bits) {
 template <int P, int KB, int VB>
 bool launch_pair(Group *g, const AppendLaunch &ak, const AppendLaunch &av) {
   constexpr size_t SMEM = ((size_t)AT_TILE * (P + 4) + (size_t)(AT_THREADS / 32) * P) * sizeof(float);
-  static bool configured[64] = {};
+  static int configured[MAX_DEVICES] = {};
   auto kern = append_pair_kernel<P, KB, VB>;
-  if (!configured[g->device & 63]) {
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM), "append");
-    configured[g->device & 63] = true;
-  }
+  if (!ensure_smem_limit(kern, configured, g->device, SMEM, "append")) return false;
   long long items = (long long)ak.heads_in_call * ak.n_tokens;
   long long tiles = (items + AT_TILE - 1) / AT_TILE;
   int gx = (int)std::min<long long>(tiles, (long long)g->sm_count * (AT_BLOCKS_PER_SM / 2));
@@ -476,12 +489,8 @@ size_t partial_floats(const CacheView &c) { return (size_t)2 + c.padded; }
 
 // The general kernel's dynamic shared memory limit only ever grows (per device).
 bool ensure_general_smem(Group *g, size_t smem) {
-  static int smem_set[64] = {};
-  if ((int)smem > smem_set[g->device & 63]) {
-    CUDA_TRY(cudaFuncSetAttribute(compute_general_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute");
-    smem_set[g->device & 63] = (int)smem;
-  }
-  return true;
+  static int smem_set[MAX_DEVICES] = {};
+  return ensure_smem_limit(compute_general_kernel, smem_set, g->device, smem, "compute");
 }
 
 bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *partial_out) {
@@ -519,7 +528,7 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   if (!direct && !fused) {
     merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
         a.partial, (size_t)items * partial_floats(c), a.n_splits, c, a.head0, a.nq,
-        want_partial_out ? partial_out : a.out, v_f32 ? 1 : 0, want_partial_out ? 1 : 0);
+        want_partial_out ? partial_out : a.out, v_f32 ? 1 : 0, want_partial_out ? 1 : 0, mirror ? a.n : 0);
     ++g_launches;
     CUDA_TRY(cudaGetLastError(), "compute (merge)");
   }
@@ -546,13 +555,10 @@ bool launch_logits(Group *g, ComputeLaunch &a, float *w, int ws) {
 template <int ITEMS>
 bool launch_sparse_fused_t(Group *g, const ComputeLaunch &a, const float *w, int ws) {
   const size_t smem = SparseSmem<ITEMS>::bytes;
-  static bool configured[64] = {};
+  static int configured[MAX_DEVICES] = {};
   auto kern = sparse_fused_kernel<ITEMS>;
-  if (!configured[g->device & 63]) {
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "compute (sparse V)");
-    configured[g->device & 63] = true;
-  }
-  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, g->c, a.head0, a.nq, a.out);
+  if (!ensure_smem_limit(kern, configured, g->device, smem, "compute (sparse V)")) return false;
+  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, a.rot, g->c, a.head0, a.nq, a.out);
   ++g_launches;
   CUDA_TRY(cudaGetLastError(), "compute (sparse V)");
   return true;
@@ -587,7 +593,7 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
   // 1. logits into the weight buffer (general kernel, mode 2)
   if (!launch_logits(g, a, w, ws)) return false;
   // 2. softmax weights, 3. stable descending sort per (head, query), 4. cut + accumulate
-  softmax_weights_kernel<<<items, CG_THREADS, 0, g->stream>>>(w, o, ws, a.n);
+  softmax_weights_kernel<<<items, CG_THREADS, 0, g->stream>>>(w, o, ws, a.n, a.rot, c.cap);
   segment_offsets_kernel<<<(items + 255) / 256, 256, 0, g->stream>>>(sb, se, items, ws, a.n);
   g_launches += 2;
   cudaError_t e = cub::DeviceSegmentedRadixSort::SortPairsDescending(base + off_t, temp_bytes, w, sw, o, so, (int)cells,
@@ -605,11 +611,8 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
 template <int KB, int KW, int VB, int VW>
 bool launch_stream_t(Group *g, const StreamLaunch &a, int grid) {
   auto kern = compute_stream_kernel<KB, KW, VB, VW>;
-  static bool configured[64] = {};
-  if (!configured[g->device & 63]) {
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CS_SMEM_BYTES), "compute");
-    configured[g->device & 63] = true;
-  }
+  static int configured[MAX_DEVICES] = {};
+  if (!ensure_smem_limit(kern, configured, g->device, CS_SMEM_BYTES, "compute")) return false;
   kern<<<grid, CS_THREADS, CS_SMEM_BYTES, g->stream>>>(a);
   ++g_launches;
   CUDA_TRY(cudaGetLastError(), "compute");
@@ -620,6 +623,21 @@ bool stream_supported(const CacheView &c) {
   if (c.padded == 128) return (c.k_bits == 4 || c.k_bits == 2) && (c.v_bits == 4 || c.v_bits == 2);
   if (c.padded == 64) return c.k_bits == 4 && c.v_bits == 4;
   return false;
+}
+
+// The streaming kernel's instantiation for a handle's shape (stream_supported() holds),
+// one persistent block per SM or per work item, whichever is fewer.
+bool launch_stream_for_shape(Group *g, const StreamLaunch &a) {
+  const CacheView &c = a.c;
+  const long long items = (long long)a.heads_in_call * a.nq * a.n_splits;
+  const int grid = (int)std::min<long long>(items, g->sm_count);
+  if (c.padded == 128) {
+    if (c.k_bits == 4 && c.v_bits == 2) return launch_stream_t<4, 16, 2, 8>(g, a, grid);
+    if (c.k_bits == 4 && c.v_bits == 4) return launch_stream_t<4, 16, 4, 16>(g, a, grid);
+    if (c.k_bits == 2 && c.v_bits == 2) return launch_stream_t<2, 8, 2, 8>(g, a, grid);
+    return launch_stream_t<2, 8, 4, 16>(g, a, grid);
+  }
+  return launch_stream_t<4, 8, 4, 8>(g, a, grid);
 }
 
 // Pick the number of KV spans per (head, query): spans are multiples of 64
@@ -648,9 +666,6 @@ void plan_spans(int n, int items_base, int sms, int &n_splits, int &span) {
   }
 }
 
-#ifdef AQ_PROBE
-static unsigned long long *g_probe = nullptr;
-#endif
 
 // Peer destinations of the next streaming launch (set by adaptq_mha_compute_partial_to_peers
 // around its call, under the handle's mutex).
@@ -662,10 +677,6 @@ bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, flo
   StreamLaunch a{};
   a.c = c; a.q = ca.q; a.out = ca.out; a.head0 = ca.head0; a.heads_in_call = ca.heads_in_call; a.nq = ca.nq;
   a.n = ca.n; a.status = g->d_status;
-#ifdef AQ_PROBE
-  if (!g_probe) { cudaMalloc(&g_probe, 256); cudaMemset(g_probe, 0, 256); }
-  a.probe = g_probe;
-#endif
   const int items_base = a.heads_in_call * a.nq;
   plan_spans(a.n, items_base, g->sm_count, a.n_splits, a.span);
   const bool direct = a.n_splits == 1 && !want_partial_out;
@@ -688,22 +699,11 @@ bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, flo
     a.n_peers = tl_peers->n; a.my_rank = tl_peers->rank;
     for (int r = 0; r < tl_peers->n; ++r) { a.peer_out[r] = tl_peers->out[r]; a.peer_flag[r] = tl_peers->flag[r]; }
   }
-  const long long items = (long long)items_base * a.n_splits;
-  const int grid = (int)std::min<long long>(items, g->sm_count);
-  bool ok;
-  if (c.padded == 128) {
-    if (c.k_bits == 4 && c.v_bits == 2) ok = launch_stream_t<4, 16, 2, 8>(g, a, grid);
-    else if (c.k_bits == 4 && c.v_bits == 4) ok = launch_stream_t<4, 16, 4, 16>(g, a, grid);
-    else if (c.k_bits == 2 && c.v_bits == 2) ok = launch_stream_t<2, 8, 2, 8>(g, a, grid);
-    else ok = launch_stream_t<2, 8, 4, 16>(g, a, grid);
-  } else {
-    ok = launch_stream_t<4, 8, 4, 8>(g, a, grid);
-  }
-  if (!ok) return false;
+  if (!launch_stream_for_shape(g, a)) return false;
   if (a.n_splits > 1 && !fused) {
     merge_partials_kernel<<<items_base, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
         a.partial, (size_t)items_base * partial_floats(c), a.n_splits, c, a.head0, a.nq,
-        want_partial_out ? partial_out : a.out, 0, want_partial_out ? 1 : 0);
+        want_partial_out ? partial_out : a.out, 0, want_partial_out ? 1 : 0, 0);
     ++g_launches;
     CUDA_TRY(cudaGetLastError(), "compute (merge)");
   }
@@ -731,6 +731,7 @@ bool compute_device(Group *g, const float *dq, float *dout, int head0, int heads
   }
   ComputeLaunch a{};
   a.c = c; a.q = dq; a.out = dout; a.head0 = head0; a.heads_in_call = heads_in_call; a.nq = nq; a.n = st.size;
+  a.rot = (int)(((long long)st.head - st.size + c.cap) % c.cap); // st.size > 0, so c.cap > 0
   a.use_mirror = (c.hyb > 0 && st.size <= c.hyb && st.mirror == st.size) ? 1 : 0;
   const bool quant = c.k_bits != 16 && c.v_bits != 16;
   if (partial_out) return launch_general_or_stream(g, a, true, dout);
@@ -1227,7 +1228,7 @@ int adaptq_mha_merge_partials(adaptq_mha_t h, const float *partials, int n_parts
   if (!ok) return -1;
   float *dout = okd == PK_DEVICE ? outs : reinterpret_cast<float *>(static_cast<char *>(g->d_stage) + off_out);
   merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
-      dp, (size_t)items * partial_floats(c), n_parts, c, 0, queries_per_head, dout, 0, 0);
+      dp, (size_t)items * partial_floats(c), n_parts, c, 0, queries_per_head, dout, 0, 0, 0);
   ++g_launches;
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess && okd != PK_DEVICE) {
@@ -1314,7 +1315,7 @@ int adaptq_mha_export_head(adaptq_mha_t h, int head_idx, uint8_t *k_rows, uint8_
 // ---------------------------------------------------------------------------
 #define AQ_STATIC_SCRATCH_BYTES (4u << 20)
 static __device__ __align__(256) float g_static_partials[AQ_STATIC_SCRATCH_BYTES / sizeof(float)];
-static float *g_static_partials_addr[64] = {};
+static float *g_static_partials_addr[MAX_DEVICES] = {};
 static std::mutex g_static_mu;
 
 int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int queries_per_head, float *outs) {
@@ -1331,7 +1332,15 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
     set_error("adaptq_mha_compute_all_static: queries and outs must be device memory (staging host buffers would allocate)");
     return -1;
   }
-  if (!stream_supported(c) || c.v_mass > 0.f || c.hyb > 0 || g->device < 0 || g->device >= 64) {
+  if (g->device < 0 || g->device >= MAX_DEVICES) {
+    set_error("adaptq_mha_compute_all_static: device ordinal %d is not supported (0..%d)", g->device, MAX_DEVICES - 1);
+    return -1;
+  }
+  if (g_policy.load() == 1) {
+    set_error("adaptq_mha_compute_all_static: kernel policy 1 (general kernels only) excludes the streaming kernel this call needs");
+    return -1;
+  }
+  if (!stream_supported(c) || c.v_mass > 0.f || c.hyb > 0) {
     set_error("adaptq_mha_compute_all_static: needs 2/4-bit K and V at head dim 64/128 (4-bit only at 64), dense V, no hybrid window");
     return -1;
   }
@@ -1375,24 +1384,10 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
   // streaming kernel first, so nothing in the array has to start at zero.
   a.partial = scratch;
   a.force_partial = 0;
-#ifdef AQ_PROBE
-  a.probe = nullptr;
-#endif
-  const long long items = (long long)items_base * a.n_splits;
-  const int grid = (int)std::min<long long>(items, g->sm_count);
-  bool ok;
-  if (c.padded == 128) {
-    if (c.k_bits == 4 && c.v_bits == 2) ok = launch_stream_t<4, 16, 2, 8>(g, a, grid);
-    else if (c.k_bits == 4 && c.v_bits == 4) ok = launch_stream_t<4, 16, 4, 16>(g, a, grid);
-    else if (c.k_bits == 2 && c.v_bits == 2) ok = launch_stream_t<2, 8, 2, 8>(g, a, grid);
-    else ok = launch_stream_t<2, 8, 4, 16>(g, a, grid);
-  } else {
-    ok = launch_stream_t<4, 8, 4, 8>(g, a, grid);
-  }
-  if (!ok) return -1;
+  if (!launch_stream_for_shape(g, a)) return -1;
   if (a.n_splits > 1) {
     merge_partials_kernel<<<items_base, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
-        scratch, (size_t)items_base * partial_floats(c), a.n_splits, c, 0, queries_per_head, outs, 0, 0);
+        scratch, (size_t)items_base * partial_floats(c), a.n_splits, c, 0, queries_per_head, outs, 0, 0, 0);
     ++g_launches;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("adaptq_mha_compute_all_static: CUDA error: %s", cudaGetErrorString(e)); return -1; }
@@ -1401,14 +1396,5 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
 }
 
 
-#ifdef AQ_PROBE
-int adaptq_probe_read(unsigned long long *out, int reset) {
-  if (!g_probe) return -1;
-  cudaDeviceSynchronize();
-  cudaMemcpy(out, g_probe, 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-  if (reset) cudaMemset(g_probe, 0, 32 * sizeof(unsigned long long));
-  return 0;
-}
-#endif
 
 } // extern "C"

@@ -47,7 +47,9 @@ static const float h_cb[3][16] = {
 //   k_scale, v_scale : [n_heads] x s_stride floats.
 //   signs  : [n_heads] x sign_words uint32; bit i set  <=>  D[i] = -1.
 //   mirror : [n_heads] x hyb x 2*dim floats (FP32 copy of the first tokens).
-//   ring_head / ring_size / mirror_cnt : [n_heads] ints, device-resident.
+//
+// The ring state (write position, live count, mirror length) lives on the host
+// and reaches the kernels as launch arguments.
 //
 // Per-head strides are multiples of 128 bytes so that any tile that starts
 // at a multiple of 16 tokens is 16-byte aligned for bulk (TMA) copies.
@@ -57,7 +59,6 @@ struct CacheView {
   float *k_scale, *v_scale;
   const uint32_t *signs;
   float *mirror;
-  int *ring_head, *ring_size, *mirror_cnt;
   size_t k_stride, v_stride, mirror_stride;
   int s_stride, sign_words;
   int n_heads, dim, padded, log2p, k_bits, v_bits, k_row, v_row, cap, hyb;
@@ -189,21 +190,36 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Returns false if the phase did not complete within the spin budget.
+// Longest time any device-side wait (ring stage, peer arrival count) may take
+// before it gives up and reports through the status word: half a second.
+constexpr unsigned long long AQ_WAIT_BUDGET_NS = 500ull * 1000ull * 1000ull;
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(addr), "r"(parity), "r"(20000u) /* suspend-time hint, ns: fewer polling rounds */
+      : "memory");
+  return done != 0;
+}
+// Returns false if the phase did not complete within AQ_WAIT_BUDGET_NS.  The
+// clock is only read once a first attempt has failed, so a wait that succeeds
+// at once costs what a bare try_wait costs.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-  uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity), "r"(20000u) /* suspend-time hint, ns: fewer polling rounds */
-        : "memory");
-    if (done) return true;
+  const uint32_t addr = smem_u32(bar);
+  if (mbar_try(addr, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    if (mbar_try(addr, parity)) return true;
+    if (global_ns() - t0 > AQ_WAIT_BUDGET_NS) return false;
   }
-  return false;
 }
 // Non-blocking: has the phase with this parity completed?
 __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {

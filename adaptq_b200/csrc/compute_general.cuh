@@ -28,6 +28,7 @@ struct ComputeLaunch {
   int w_stride;
   int head0, heads_in_call, nq;
   int n;        // live tokens (same for every head of the call)
+  int rot;      // ring slot of the oldest live token: logical position i sits in slot (rot + i) % capacity
   int use_mirror;
   int n_splits, span; // tokens per split
   int chunk;          // tokens per shared-memory pass
@@ -59,23 +60,29 @@ __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) 
 // [n_parts][items][2+P] with part stride `part_stride` floats.
 // One block (CG_THREADS threads) merges the n_parts partials of `item`; vec: P floats of shared memory.
 // Partials are read past L1 (__ldcg): other blocks of the same launch may have written them.
+//
+// Non-finite values travel as they do upstream (attention/attention.cpp:422-429 has no
+// guard): a part whose sum is NaN makes the result NaN, a part whose weight underflows
+// to zero still contributes 0 * acc.  Only a part marked empty -- max == -inf, which no
+// span with tokens produces because the running maximum starts at -1e30f as upstream's
+// does -- is skipped (its accumulator was never written).  guard_n > 0 selects the
+// hybrid window's rule (attention.cpp:513): a sum that is zero or not finite is
+// replaced by guard_n, i.e. the weights become exp(..)/n.
 __device__ __forceinline__ void merge_partials_block(const float *parts, size_t part_stride, int n_parts, const CacheView &c,
-                                                     int item, int h, float *out, int v_f32, int to_partial, float *vec) {
+                                                     int item, int h, float *out, int v_f32, int to_partial, float *vec,
+                                                     int guard_n) {
   const int P = c.padded, dim = c.dim;
   const int tid = threadIdx.x;
   const float *base = parts + (size_t)item * (2 + P);
   // All loads of a step are independent of each other, so their latencies
   // overlap: the (max, sum) pairs are read one part per thread, the
   // accumulators with the parts dealt round-robin to thread groups.
-  __shared__ float s_w[1024];        // weight exp(m_p - M) of the first 1024 parts
+  __shared__ float s_w[1024];        // weight exp(m_p - M) of the first 1024 parts; -1 marks an empty part
   __shared__ float s_red[CG_WARPS];
   __shared__ float s_grp[CG_THREADS];
   const int lane = tid & 31, warp = tid >> 5;
   float m_loc = -INFINITY;
-  for (int p = tid; p < n_parts; p += CG_THREADS) {
-    const float *pp = base + (size_t)p * part_stride;
-    if (__ldcg(pp + 1) > 0.f) m_loc = fmaxf(m_loc, __ldcg(pp));
-  }
+  for (int p = tid; p < n_parts; p += CG_THREADS) m_loc = fmaxf(m_loc, __ldcg(base + (size_t)p * part_stride));
   m_loc = warp_max(m_loc);
   if (lane == 0) s_red[warp] = m_loc;
   __syncthreads();
@@ -85,21 +92,25 @@ __device__ __forceinline__ void merge_partials_block(const float *parts, size_t 
   float l_loc = 0.f;
   for (int p = tid; p < n_parts; p += CG_THREADS) {
     const float *pp = base + (size_t)p * part_stride;
-    const float l = __ldcg(pp + 1);
-    const float w = l > 0.f ? expf(__ldcg(pp) - M) : 0.f;
+    const float m = __ldcg(pp);
+    const bool live = m != -INFINITY;
+    const float w = live ? expf(m - M) : -1.f;
     if (p < 1024) s_w[p] = w;
-    l_loc += l > 0.f ? l * w : 0.f;
+    if (live) l_loc += __ldcg(pp + 1) * w;
   }
   l_loc = warp_sum(l_loc);
   if (lane == 0) s_red[warp] = l_loc;
   __syncthreads(); // also publishes s_w
   float L = 0.f;
   for (int w = 0; w < CG_WARPS; ++w) L += s_red[w];
-  const float invL = to_partial ? 1.f : 1.f / L;
+  float invL = 1.f / L;
+  if (guard_n > 0 && !(L > 0.f && L < INFINITY)) invL = 1.f / (float)guard_n;
+  if (to_partial) invL = 1.f;
+  if (M == -INFINITY) invL = 0.f; // every part is empty: zeros, as for an empty cache
   auto weight = [&](int p) -> float {
     if (p < 1024) return s_w[p];
-    const float *pp = base + (size_t)p * part_stride;
-    return __ldcg(pp + 1) > 0.f ? expf(__ldcg(pp) - M) : 0.f;
+    const float m = __ldcg(base + (size_t)p * part_stride);
+    return m != -INFINITY ? expf(m - M) : -1.f;
   };
   if (P <= CG_THREADS) {
     const int groups = CG_THREADS / P, g = tid / P, j = tid % P;
@@ -108,8 +119,7 @@ __device__ __forceinline__ void merge_partials_block(const float *parts, size_t 
 #pragma unroll 8
       for (int p = g; p < n_parts; p += groups) {
         const float w = weight(p);
-        const float v = w > 0.f ? __ldcg(base + (size_t)p * part_stride + 2 + j) : 0.f;
-        s += v * w;
+        if (w != -1.f) s += __ldcg(base + (size_t)p * part_stride + 2 + j) * w;
       }
     }
     s_grp[tid] = s;
@@ -125,8 +135,7 @@ __device__ __forceinline__ void merge_partials_block(const float *parts, size_t 
 #pragma unroll 8
       for (int p = 0; p < n_parts; ++p) {
         const float w = weight(p);
-        const float v = w > 0.f ? __ldcg(base + (size_t)p * part_stride + 2 + j) : 0.f;
-        s += v * w;
+        if (w != -1.f) s += __ldcg(base + (size_t)p * part_stride + 2 + j) * w;
       }
       vec[j] = s * invL;
     }
@@ -151,11 +160,11 @@ __device__ __forceinline__ void merge_partials_block(const float *parts, size_t 
 
 __global__ void __launch_bounds__(CG_THREADS) merge_partials_kernel(
     const float *parts, size_t part_stride, int n_parts, CacheView c, int head0, int nq, float *out,
-    int v_f32, int to_partial) {
+    int v_f32, int to_partial, int guard_n) {
   extern __shared__ __align__(16) unsigned char smem_gen[];
   const int item = blockIdx.x; // hl*nq + qi
   merge_partials_block(parts, part_stride, n_parts, c, item, head0 + item / nq, out, v_f32, to_partial,
-                       reinterpret_cast<float *>(smem_gen));
+                       reinterpret_cast<float *>(smem_gen), guard_n);
 }
 
 __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const ComputeLaunch a) {
@@ -218,7 +227,9 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   const int tg = P < CG_THREADS ? tid / P : 0;
   constexpr int MAXR = 4; // P <= 1024
   float acc[MAXR] = {0.f, 0.f, 0.f, 0.f};
-  float run_m = -INFINITY, run_l = 0.f;
+  // the running maximum starts where upstream's does (attention.cpp:384, :498, :566): logits
+  // below it (or NaN) never become the maximum, and their weights come out as upstream's do
+  float run_m = -1e30f, run_l = 0.f;
   const float *vcb = v_f32 ? nullptr : c_cb[c.v_bits - 2];
 
   for (int t0 = t_begin; t0 < t_end; t0 += a.chunk) {
@@ -239,9 +250,14 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
       if (lane == 0) sc[i] = k_f32 ? sum * attn_s : sum * attn_s * ksc[s];
     }
     __syncthreads();
-    if (a.mode == 2) { // raw logits out; normalised later by softmax_weights_kernel
+    if (a.mode == 2) { // raw logits out, stored by LOGICAL position (oldest token first, as upstream
+      // walks them, attention.cpp:562-563) so that the later sort breaks ties the same way
       float *w = a.weights + ((size_t)hl * a.nq + qi) * a.w_stride;
-      for (int i = tid; i < cn; i += CG_THREADS) w[t0 + i] = sc[i];
+      for (int i = tid; i < cn; i += CG_THREADS) {
+        int pos = t0 + i - a.rot;
+        if (pos < 0) pos += c.cap;
+        w[pos] = sc[i];
+      }
       __syncthreads();
       continue;
     }
@@ -250,7 +266,7 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
     for (int i = tid; i < cn; i += CG_THREADS) mx = fmaxf(mx, sc[i]);
     mx = block_reduce(mx, red, true);
     const float new_m = fmaxf(run_m, mx);
-    const float rescale = (run_m == -INFINITY) ? 0.f : expf(run_m - new_m);
+    const float rescale = expf(run_m - new_m);
     float ls = 0.f;
     for (int i = tid; i < cn; i += CG_THREADS) {
       float e = expf(sc[i] - new_m);
@@ -323,11 +339,14 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
     if (!s_last) return;
     if (tid == 0) a.counters[item] = 0;
     __threadfence();
-    merge_partials_block(a.partial, part_stride, a.n_splits, c, item, h, a.final_out, v_f32 ? 1 : 0, a.final_to_partial, vec);
+    merge_partials_block(a.partial, part_stride, a.n_splits, c, item, h, a.final_out, v_f32 ? 1 : 0, a.final_to_partial, vec,
+                         mirror ? a.n : 0);
     return;
   }
   // ---- normalise, inverse transform, write ----------------------------------------
-  const float invl = 1.f / run_l;
+  // the hybrid window replaces a zero or non-finite sum by n (attention.cpp:513); the other
+  // branches divide by whatever the sum is (:428, :582)
+  const float invl = (mirror && !(run_l > 0.f && run_l < INFINITY)) ? 1.f / (float)a.n : 1.f / run_l;
   float *o = a.out + ((size_t)hl * a.nq + qi) * dim;
   if (v_f32) {
     for (int j = tid; j < dim; j += CG_THREADS) o[j] = vec[j] * invl;
@@ -349,7 +368,7 @@ __device__ __forceinline__ void peers_finish(const float *base, size_t part_stri
   for (int e = 0; e < EPL; ++e) v[e] = 0.f;
   for (int r = 0; r < world; ++r) {
     const float w = __shfl_sync(0xffffffffu, w_p, r);
-    if (w > 0.f) {
+    if (w != -1.f) { // -1 marks a rank without tokens
 #pragma unroll
       for (int e = 0; e < EPL; ++e) v[e] += w * __ldcg(base + (size_t)r * part_stride + 2 + EPL * lane + e);
     }
@@ -368,7 +387,7 @@ __device__ __forceinline__ void peers_finish(const float *base, size_t part_stri
 // (parts laid out [world][items][2+P]).  Rank r's kernel adds 1 to flags[r] (system
 // scope, with release semantics) for every item it has delivered; `expected` is the
 // running total this step must reach.  The wait is bounded: if a peer's count does
-// not arrive within the spin budget the warp records status 3, writes zeros and
+// not arrive within AQ_WAIT_BUDGET_NS the warp records status 3, writes zeros and
 // returns, so a lost peer costs an error code, never a hang.
 __global__ void __launch_bounds__(128) merge_peers_kernel(
     const float *parts, size_t part_stride, int world, const unsigned int *flags, unsigned int expected, int *status,
@@ -381,11 +400,12 @@ __global__ void __launch_bounds__(128) merge_peers_kernel(
   int ok = 1;
   if (lane < world) {
     unsigned int seen = 0;
-    int spins = 0;
-    for (;;) {
+    unsigned long long t0 = 0;
+    for (int spins = 0;; ++spins) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + lane) : "memory");
       if ((int)(seen - expected) >= 0) break;       // counts only grow; compare modulo 2^32
-      if (++spins > (1 << 20)) { ok = 0; break; }   // about a quarter of a second
+      if (spins == 0) t0 = global_ns();
+      else if (global_ns() - t0 > AQ_WAIT_BUDGET_NS) { ok = 0; break; }
       __nanosleep(100);
     }
   }
@@ -397,15 +417,17 @@ __global__ void __launch_bounds__(128) merge_peers_kernel(
     return;
   }
   const float *base = parts + (size_t)item * (2 + P);
+  // same rules as merge_partials_block: only a rank that delivered (-inf, 0) is skipped
   float m_p = -INFINITY, l_p = 0.f;
   if (lane < world) {
+    m_p = __ldcg(base + (size_t)lane * part_stride);
     l_p = __ldcg(base + (size_t)lane * part_stride + 1);
-    if (l_p > 0.f) m_p = __ldcg(base + (size_t)lane * part_stride);
   }
   const float M = warp_max(m_p);
-  const float w_p = l_p > 0.f ? expf(m_p - M) : 0.f;
-  const float L = warp_sum(l_p > 0.f ? l_p * w_p : 0.f);
-  const float invL = 1.f / L;
+  const bool live = m_p != -INFINITY;
+  const float w_p = live ? expf(m_p - M) : -1.f;
+  const float L = warp_sum(live ? l_p * w_p : 0.f);
+  const float invL = M == -INFINITY ? 0.f : 1.f / L;
   const uint32_t *sg = c.signs + (size_t)(head0 + item / nq) * c.sign_words;
   const float isp = 1.f / sqrtf((float)P);
   // the usual sizes: in registers, butterflies with shuffles (lane l owns elements EPL*l .. EPL*l+EPL-1)
@@ -418,7 +440,7 @@ __global__ void __launch_bounds__(128) merge_peers_kernel(
     float sacc = 0.f;
     for (int r = 0; r < world; ++r) {
       const float w = __shfl_sync(0xffffffffu, w_p, r);
-      if (w > 0.f) sacc += w * __ldcg(base + (size_t)r * part_stride + 2 + j);
+      if (w != -1.f) sacc += w * __ldcg(base + (size_t)r * part_stride + 2 + j);
     }
     vec[j] = sacc * invL;
   }
@@ -442,7 +464,8 @@ __global__ void __launch_bounds__(128) merge_peers_kernel(
 // Step 1 (this kernel): logits -> weights e*(1/sum) in place, plus the token
 // index list for the sort.  One block per (head, query).
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(CG_THREADS) softmax_weights_kernel(float *weights, int *order, int w_stride, int n) {
+__global__ void __launch_bounds__(CG_THREADS) softmax_weights_kernel(float *weights, int *order, int w_stride, int n,
+                                                                     int rot, int cap) {
   __shared__ float red[64];
   float *w = weights + (size_t)blockIdx.x * w_stride;
   int *o = order + (size_t)blockIdx.x * w_stride;
@@ -460,7 +483,7 @@ __global__ void __launch_bounds__(CG_THREADS) softmax_weights_kernel(float *weig
   const float inv = 1.f / s;
   for (int i = tid; i < n; i += CG_THREADS) {
     w[i] *= inv;
-    o[i] = i;
+    o[i] = i + rot < cap ? i + rot : i + rot - cap; // logical position -> ring slot
   }
 }
 

@@ -6,7 +6,10 @@
 // (descending), accumulate V rows in blocks of four while four remain and the
 // running mass is below v_mass, then singles; weights are not renormalised.
 //
-// The logits come from compute_general_kernel (mode 2).  Here: softmax in
+// The logits come from compute_general_kernel (mode 2), ordered oldest token
+// first like upstream's slot list (attention.cpp:562-563), so equal weights keep
+// that order through the stable sort -- the order a stable sort of upstream's
+// list would give (upstream's std::sort leaves ties unspecified).  Here: softmax in
 // registers, a stable block-wide radix sort of (weight, token) pairs, the
 // block sums ((w0+w1)+w2)+w3 in parallel and the running mass sequentially in
 // upstream's association (so the cut is the one a sequential walk finds), then
@@ -42,7 +45,7 @@ __device__ __forceinline__ float sp_block_reduce(float v, float *red, bool is_ma
 }
 
 template <int ITEMS>
-__global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *logits, int w_stride, int n, CacheView c,
+__global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *logits, int w_stride, int n, int rot, CacheView c,
                                                                   int head0, int nq, float *out) {
   using S = SparseSmem<ITEMS>;
   using Sort = typename S::Sort;
@@ -69,7 +72,7 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   for (int k = 0; k < ITEMS; ++k) {
     const int i = tid * ITEMS + k;
     key[k] = i < n ? lg[i] : -INFINITY;
-    val[k] = i;
+    val[k] = i + rot < c.cap ? i + rot : i + rot - c.cap; // logits are in logical order; the V rows are read by slot
     mx = fmaxf(mx, key[k]);
   }
   mx = sp_block_reduce(mx, red, true);

@@ -44,19 +44,6 @@
 
 namespace aq {
 
-// -DAQ_PROBE=1 builds a diagnostic variant that accumulates per-phase cycle counts
-// (thread 0 of each block) into StreamLaunch::probe; 2 adds per-wait timing.
-#ifdef AQ_PROBE
-#define AQ_MARK(k)                                     \
-  if (tid == 0) {                                      \
-    long long now__ = clock64();                       \
-    probe_acc[k] += (unsigned long long)(now__ - probe_last); \
-    probe_last = now__;                                \
-  }
-#else
-#define AQ_MARK(k)
-#endif
-
 constexpr int CS_CONSUMERS = 512;           // 16 consumer warps
 constexpr int CS_WARPS = CS_CONSUMERS / 32;
 constexpr int CS_HELPER_TID = CS_CONSUMERS + 32;
@@ -90,9 +77,6 @@ struct StreamLaunch {
   int n_peers, my_rank;
   float *peer_out[8];
   unsigned int *peer_flag[8];
-#ifdef AQ_PROBE
-  unsigned long long *probe; // per-phase cycle counters (diagnostic builds only)
-#endif
 };
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CS_CONSUMERS) : "memory"); }
@@ -110,8 +94,11 @@ __device__ __forceinline__ void red_shared_add(uint32_t addr, uint32_t v) {
 // exp(x) for x <= 0 from the hardware 2^t unit, with the rounding error of
 // t = x*log2(e) (and the part of log2(e) a float cannot hold) put back through
 // exp(x) = 2^t * (1 + r*ln 2): relative error ~2^-22, a third of the instructions of expf.
+// Arguments below -200 (the result underflows long before) are clamped so that
+// -inf gives 0 instead of inf - inf; NaN stays NaN.
 __device__ __forceinline__ float exp_nonpos(float x) {
   const float L2E_HI = 1.4426950216293335f, L2E_LO = 1.9259629911266175e-8f;
+  x = x < -200.f ? -200.f : x;
   const float t = x * L2E_HI;
   const float r = fmaf(x, L2E_HI, -t) + x * L2E_LO;
   float e;
@@ -440,11 +427,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
             __threadfence();
             const size_t pstride = (size_t)items_base * (size_t)(2 + P);
             const float *base = a.partial + (size_t)hq * (size_t)(2 + P);
+            // same rules as merge_partials_block: NaN sums and zero weights travel as
+            // they do upstream; every span of this launch holds tokens, so none is skipped
             float M = -INFINITY;
-            for (int p = lane; p < a.n_splits; p += 32) {
-              const float *q2 = base + (size_t)p * pstride;
-              if (__ldcg(q2 + 1) > 0.f) M = fmaxf(M, __ldcg(q2));
-            }
+            for (int p = lane; p < a.n_splits; p += 32) M = fmaxf(M, __ldcg(base + (size_t)p * pstride));
             M = warp_max(M);
             float L = 0.f, am[EPL];
 #pragma unroll
@@ -454,9 +440,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
               float w = 0.f;
               if (p < a.n_splits) {
                 const float *q2 = base + (size_t)p * pstride;
-                const float l = __ldcg(q2 + 1);
-                w = l > 0.f ? expf(__ldcg(q2) - M) : 0.f;
-                L += l > 0.f ? l * w : 0.f;
+                w = expf(__ldcg(q2) - M);
+                L += __ldcg(q2 + 1) * w;
               }
               const int cnt = min(32, a.n_splits - p0);
 #pragma unroll 4
@@ -465,7 +450,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
                 const float2 *row = reinterpret_cast<const float2 *>(base + (size_t)(p0 + j) * pstride + 2 + EPL * lane);
 #pragma unroll
                 for (int e = 0; e < EPL / 2; ++e) {
-                  const float2 x = wj > 0.f ? __ldcg(row + e) : make_float2(0.f, 0.f);
+                  const float2 x = __ldcg(row + e);
                   am[2 * e] += wj * x.x;
                   am[2 * e + 1] += wj * x.y;
                 }
@@ -549,16 +534,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 
   int stage = 0;
   uint32_t phase = 0;
-#ifdef AQ_PROBE
-  unsigned long long probe_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  unsigned long long probe_mywait = 0;
-  unsigned long long probe_hist[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  long long probe_last = clock64();
-  unsigned long long probe_gt0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(probe_gt0));
-  const long long probe_c0 = probe_last;
-  int probe_phase = 5;
-#endif
   bool next_ready = false;
   // Poll the barrier of the stage after the current one without blocking; the
   // answer is used by the next wait_full(), so the poll's latency (it queues
@@ -569,24 +544,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     next_ready = mbar_test(&full[ns], np);
   };
   auto wait_full = [&]() {
-#if defined(AQ_PROBE) && AQ_PROBE > 1
-    const long long w0__ = clock64();
-#endif
     // The stage was already tested (peek_next) while the previous tile was being
     // processed; only a stage that had not landed by then is waited for here.
     if (!next_ready && *reinterpret_cast<volatile int *>(s_fail) == 0 && !mbar_wait(&full[stage], phase)) {
       *reinterpret_cast<volatile int *>(s_fail) = 1;
       atomicExch(a.status, 1);
     }
-#if defined(AQ_PROBE) && AQ_PROBE > 1
-    if (tid == 0) {
-      const unsigned long long dt__ = (unsigned long long)(clock64() - w0__);
-      probe_acc[probe_phase] += dt__;
-      const int bin__ = dt__ < 100 ? 0 : dt__ < 500 ? 1 : dt__ < 2000 ? 2 : 3;
-      probe_hist[bin__] += 1; probe_hist[4 + bin__] += dt__;
-    }
-    probe_mywait += (unsigned long long)(clock64() - w0__);
-#endif
   };
   auto release = [&]() {
     __syncwarp();
@@ -648,11 +611,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     consumer_sync();
     if (tid == 0) mbar_arrive(&qempty[qb]); // every thread has read the rotated query
     }
-
-    AQ_MARK(0)
-#ifdef AQ_PROBE
-    probe_phase = 5;
-#endif
     // ---- K stream: logits into sc[] ----------------------------------------------------
     // After the group reduction one lane per token owns its dot product; that lane
     // also reads the token's K scale (it arrived with the stage) and keeps a running
@@ -661,7 +619,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     const int own_step = KLPT == 4 ? (KSTEPS == 4 ? kwl : (kwl >> 1)) : (KSTEPS == 8 ? wl : (wl >> 1));
     const bool owner = KLPT == 4 ? (KSTEPS == 4 || (kwl & 1) == 0) : (KSTEPS == 8 || (wl & 1) == 0);
     const int own_tok = warp * (TKN / CS_WARPS) + KTPS * own_step + kg;
-    float lane_max = -INFINITY;
+    float lane_max = -1e30f; // where upstream's running maximum starts (attention.cpp:384)
     for (int t = t0; t < t1; t += TKN) {
       wait_full();
       const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
@@ -723,7 +681,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         for (int rr = 0; rr < RPS; ++rr) vv[cchunk * RPS + rr] = 0.f;
       }
     }
-    AQ_MARK(1)
     const float mx = consumer_max(lane_max, red_max); // its barrier also publishes sc[]
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
@@ -741,8 +698,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     consumer_sum2(ls, wsum, red_sum);
     // weights -> 32-bit fixed point with the span's total mapped to 2^30, so no
     // bucket can overflow and the rounding error is below 2^-31 of the total per token
+    // A total that is NaN or infinite (a NaN logit, an infinite V scale) makes the
+    // accumulator NaN, as upstream's floating-point sums would be.
     const float fx = (wsum > 0.f && wsum < INFINITY) ? 1073741824.0f / wsum : 0.f;
-    const float inv_fx = fx > 0.f ? wsum * (1.0f / 1073741824.0f) : 0.f;
+    const float inv_fx = fx > 0.f ? wsum * (1.0f / 1073741824.0f) : (wsum == 0.f ? 0.f : __int_as_float(0x7fc00000));
     uint32_t *scu = reinterpret_cast<uint32_t *>(sc);
     const int len_pad = min(CS_SPAN_MAX, (len + TVN - 1) / TVN * TVN);
     // Stored in the order the V stream reads them: the VSTEPS weights that one lane
@@ -758,11 +717,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       if (i < len_pad) scu[i + shift] = __float2uint_rn(sv[r] * fx);
     }
     consumer_sync();
-
-    AQ_MARK(2)
-#ifdef AQ_PROBE
-    probe_phase = 6;
-#endif
     // ---- V stream: add each token's weight into bucket[byte][column] ---------------------
     for (int t = t0; t < t1; t += TVN) {
       wait_full();
@@ -795,8 +749,6 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       release();
     }
     consumer_sync();
-
-    AQ_MARK(3)
     // ---- buckets -> rotated-domain accumulator -------------------------------------------
     // acc[j] = sum over byte values of bucket[byte][column(j)] * centroid[digit_j(byte)].
     // A thread owns one byte column and a slice of the 256 byte values, reads each
@@ -865,21 +817,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         if (lane == 0) mbar_arrive(&afull[ab]);
       }
     }
-    AQ_MARK(4)
   }
-#ifdef AQ_PROBE
-  if (tid == 0 && a.probe)
-    for (int k = 0; k < 7; ++k) atomicAdd(a.probe + k, probe_acc[k]);
-  if (tid == 0 && blockIdx.x == 0 && a.probe) { // SM clock seen by block 0: cycles / nanoseconds
-    unsigned long long gt1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
-    a.probe[7] = gt1 - probe_gt0;
-    a.probe[30] = (unsigned long long)(clock64() - probe_c0);
-  }
-  if (lane == 0 && a.probe) atomicAdd(a.probe + 8 + warp, probe_mywait);
-  if (tid == 0 && a.probe)
-    for (int k = 0; k < 8; ++k) atomicAdd(a.probe + 24 + k, probe_hist[k]);
-#endif
 }
 
 } // namespace aq

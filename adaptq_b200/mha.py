@@ -27,6 +27,10 @@ def _as_arg(x, shape_check=None):
     return C.c_void_p(a.ctypes.data), a, False
 
 
+def _is_cuda_tensor(x) -> bool:
+    return torch is not None and isinstance(x, torch.Tensor) and x.is_cuda
+
+
 class MHAContext:
     """n_heads independent quantized KV caches on the current CUDA device.
 
@@ -56,6 +60,27 @@ class MHAContext:
         info = _lib.MhaInfo()
         L.adaptq_mha_info(self._h, C.byref(info))
         self.info = info
+        self._stream = 0  # the CUDA stream the library launches on (0: the legacy default stream)
+
+    def _adopt(self, *tensors):
+        """Before a call that takes CUDA tensors: they must live on the handle's
+        device, and the library must launch on the stream PyTorch is currently
+        using -- otherwise, under torch.cuda.stream(s), its kernels could read
+        inputs that are not produced yet, the caller could read outputs that are
+        not written yet, and temporaries made here could be recycled by the
+        caching allocator while a kernel still reads them."""
+        dev = None
+        for t in tensors:
+            if _is_cuda_tensor(t):
+                idx = t.device.index if t.device.index is not None else torch.cuda.current_device()
+                if idx != self.info.device:
+                    raise ValueError(f"CUDA tensor on device {idx}, but this cache lives on device {self.info.device}")
+                dev = idx
+        if dev is None:
+            return
+        stream = int(torch.cuda.current_stream(dev).cuda_stream)
+        if stream != self._stream:
+            self.set_stream(stream)
 
     def close(self):
         if getattr(self, "_h", None):
@@ -115,13 +140,17 @@ class MHAContext:
     def append_all(self, keys, vals, pos0=0):
         """keys, vals: [n_tokens, n_heads, dim] (or [n_heads, dim] for one token);
         numpy (host) or torch (host / CUDA) float32."""
+        self._adopt(keys, vals)
         kp, kk, _ = _as_arg(keys)
         vp, vk, _ = _as_arg(vals)
         shape = tuple(kk.shape)
+        vshape = tuple(vk.shape)
         if len(shape) == 2:
             shape = (1,) + shape
-        if len(shape) != 3 or shape[1] != self._n_heads or shape[2] != self._head_dim or tuple(vk.shape)[-2:] != shape[-2:]:
-            raise ValueError(f"keys and vals must be shape (T, {self._n_heads}, {self._head_dim})")
+        if len(vshape) == 2:
+            vshape = (1,) + vshape
+        if len(shape) != 3 or shape[1] != self._n_heads or shape[2] != self._head_dim or vshape != shape:
+            raise ValueError(f"keys and vals must both be shape (T, {self._n_heads}, {self._head_dim})")
         rc = self._L.adaptq_mha_append_batch(self._h, kp, vp, shape[0], pos0)
         if rc != 0:
             raise RuntimeError(_lib.last_error())
@@ -129,6 +158,7 @@ class MHAContext:
     def compute_all(self, queries, out=None):
         """queries: [n_heads, dim] or [n_heads, nq, dim].  Returns an array/tensor of
         the same shape, on the same device as `queries`."""
+        self._adopt(queries, out)
         qp, qk, is_dev = _as_arg(queries)
         shape = tuple(qk.shape)
         nq = 1 if len(shape) == 2 else shape[1]
@@ -146,6 +176,7 @@ class MHAContext:
         """One decode step for all heads: append keys/vals [n_heads, dim], then attend
         with queries [n_heads, dim].  Same result as append_all + compute_all; with
         page-locked host arrays the transfers overlap the kernels."""
+        self._adopt(keys, vals, queries, out)
         kp, kk, _ = _as_arg(keys)
         vp, vk, _ = _as_arg(vals)
         qp, qk, _ = _as_arg(queries)
@@ -161,6 +192,7 @@ class MHAContext:
 
     def compute_partial(self, queries, out=None):
         """Un-normalised split-KV partials [n_heads, nq, 2+padded] for sequence sharding."""
+        self._adopt(queries, out)
         qp, qk, _ = _as_arg(queries)
         shape = tuple(qk.shape)
         nq = 1 if len(shape) == 2 else shape[1]
@@ -178,6 +210,7 @@ class MHAContext:
     def compute_partial_to_peers(self, queries, peer_buf_ptrs, peer_flag_ptrs, rank):
         """Split-KV partials stored straight into every rank's gather buffer (device
         addresses as mapped in this process) -- see adaptq_mha_compute_partial_to_peers."""
+        self._adopt(queries)
         qp, qk, _ = _as_arg(queries)
         shape = tuple(qk.shape)
         nq = 1 if len(shape) == 2 else shape[1]
@@ -190,7 +223,9 @@ class MHAContext:
     def merge_from_peers(self, gather_buf_ptr, flags_ptr, world, expected, nq=1, out=None):
         """Wait for every rank's arrival count to reach `expected`, merge, write [n_heads, nq, dim]."""
         if out is None:
-            out = torch.empty((self._n_heads, nq, self._head_dim), dtype=torch.float32, device="cuda")
+            out = torch.empty((self._n_heads, nq, self._head_dim), dtype=torch.float32,
+                              device=torch.device("cuda", self.info.device))
+        self._adopt(out)
         op, ok, _ = _as_arg(out)
         rc = self._L.adaptq_mha_merge_from_peers(self._h, C.c_void_p(int(gather_buf_ptr)), C.c_void_p(int(flags_ptr)), world,
                                                  C.c_uint(expected & 0xFFFFFFFF), nq, op)
@@ -200,6 +235,7 @@ class MHAContext:
 
     def merge_partials(self, partials, nq=1, out=None):
         """partials: [n_parts, n_heads, nq, 2+padded] -> [n_heads, nq, dim]."""
+        self._adopt(partials, out)
         pp, pk, _ = _as_arg(partials)
         n_parts = pk.shape[0]
         if out is None:
@@ -213,7 +249,10 @@ class MHAContext:
         return ok
 
     def set_stream(self, cuda_stream_ptr):
+        """Launch this handle's work on the given CUDA stream from now on (the library
+        first waits for what it queued on the previous one)."""
         self._L.adaptq_mha_set_stream(self._h, C.c_void_p(cuda_stream_ptr))
+        self._stream = int(cuda_stream_ptr or 0)
 
     def synchronize(self):
         if self._L.adaptq_mha_synchronize(self._h) != 0:

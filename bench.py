@@ -22,6 +22,12 @@ The line also carries:
   roofline     streaming decode kernel: algorithmic KV bytes / measured kernel time
                against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
   append       bulk-append kernel throughput (vectors/s) and its roofline
+  longctx      the long-context configuration (one 131072-token sequence, 32 KV heads, K2/V2
+               and K4/V4) with its KV range split over the N ranks (strong scaling): us per
+               decode step, the local kernels' share, the exchange's share, one head checked
+               against the CPU oracle ("sharded_check")
+  parity_sample  four head-instances of the timed cache re-run on the CPU oracle outside the
+               timed region: packed rows bit-exact, one step's outputs within tolerance
   cpu_baseline the upstream CPU implementation on this host's cores (bounded sample)
 """
 from __future__ import annotations
@@ -87,6 +93,9 @@ def parse():
                          "them into every rank's buffer over NVLink (torch symmetric memory)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-append-bench", action="store_true")
+    ap.add_argument("--skip-longctx", action="store_true", help="leave the long-context measurement out of the default line")
+    ap.add_argument("--skip-parity-sample", action="store_true")
+    ap.add_argument("--longctx-steps", type=int, default=20)
     ap.add_argument("--cpu-sample-heads", type=int, default=0)
     return ap.parse_args()
 
@@ -96,7 +105,7 @@ def measured_peak():
     try:
         return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, an earlier measurement of the same copy on a B200)"
 
 
 # --------------------------------------------------------------------------
@@ -156,7 +165,9 @@ class ClockSampler:
 def cpu_arm(n_heads_sample: int, context: int, steps: int, warmup: int, seqs: int, threads: int):
     """Times the upstream CPU build on `n_heads_sample` head-instances of the same
     shape and distribution, scales linearly to the full head count (heads are
-    independent).  Returns (tokens_per_s, description dict)."""
+    independent).  One CPU step = what one GPU step is: append one token to every
+    head of the sample (full ring, so it evicts) + one query per head.  Also times a
+    single thread on a few heads.  Returns (tokens_per_s, description dict)."""
     import numpy as np
     from oracle import loader
     kind = "reference" if loader.ref_available(fast=True) else "port"
@@ -169,11 +180,15 @@ def cpu_arm(n_heads_sample: int, context: int, steps: int, warmup: int, seqs: in
         a[m] = (rng.standard_normal(int(m.sum())) * 20.0).astype(np.float32)
     q = rng.standard_normal((n_heads_sample, DIM), dtype=np.float32)
     total_heads = seqs * LAYERS * KV_HEADS
+    one_thread = None
     if kind == "reference":
         loader.time_reference_heads(min(n_heads_sample, threads), DIM, K_BITS, V_BITS, 64, 42,
                                     keys[:threads, :64], vals[:threads, :64], q[:threads], max(1, warmup), threads)
         t_app, t_cmp, _ = loader.time_reference_heads(n_heads_sample, DIM, K_BITS, V_BITS, context, 42, keys, vals, q,
                                                       steps, threads)
+        n1 = min(4, n_heads_sample)
+        _, t1, _ = loader.time_reference_heads(n1, DIM, K_BITS, V_BITS, context, 42, keys[:n1], vals[:n1], q[:n1], steps, 1)
+        one_thread = seqs / ((t1 / steps) * (total_heads / n1))
     else:  # the C restatement, single thread
         threads = 1
         O = loader.oracle()
@@ -183,16 +198,22 @@ def cpu_arm(n_heads_sample: int, context: int, steps: int, warmup: int, seqs: in
             hd.append_many(keys[h], vals[h])
         t_app = time.perf_counter() - t0
         t0 = time.perf_counter()
-        for _ in range(steps):
+        for s_ in range(steps):
             for h, hd in enumerate(hs):
+                hd.append(keys[h, s_ % context], vals[h, s_ % context])
                 hd.compute(q[h])
         t_cmp = time.perf_counter() - t0
     step_s = (t_cmp / steps) * (total_heads / n_heads_sample)
     tok_s = seqs / step_s
+    sample_mb = n_heads_sample * context * (DIM * K_BITS // 8 + DIM * V_BITS // 8 + 8) / 1e6
     desc = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": kind,
             "sample": f"{n_heads_sample} of {total_heads} head-instances (dim {DIM}, context {context}, K{K_BITS}/V{V_BITS}, "
-                      f"dense V), {steps} compute steps, scaled linearly by head count; "
-                      f"append {2 * n_heads_sample * context / t_app:.3g} vectors/s on the same cores",
+                      f"dense V), {steps} decode steps (append 1 token per head into the full ring + 1 query per head), "
+                      f"one worker per head on {threads} threads, scaled linearly by head count; the sample's packed cache "
+                      f"is {sample_mb:.0f} MB (the full one is {sample_mb * total_heads / n_heads_sample / 1e3:.1f} GB), so it "
+                      f"enjoys more of the host's caches than the full job would; bulk append "
+                      f"{2 * n_heads_sample * context / t_app:.3g} vectors/s on the same cores",
+            "value_one_thread": one_thread,
             "append_vectors_per_s": 2 * n_heads_sample * context / t_app,
             "ms_per_step_scaled": step_s * 1e3}
     return tok_s, desc
@@ -213,7 +234,7 @@ def run_reference(args):
     if rank != 0:
         return
     threads = host_threads()
-    n_sample = args.cpu_sample_heads or max(threads, 32)
+    n_sample = args.cpu_sample_heads or max(2 * threads, 64)
     tok_s, desc = cpu_arm(n_sample, args.context, max(1, args.steps), args.warmup, args.seqs, threads)
     line = {"impl": "reference", "metric": "decode_attn_tokens_per_s", "value": tok_s, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": desc["ms_per_step_scaled"],
@@ -234,9 +255,14 @@ def workload_config(args):
 # --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
-def fill_cache(ctx, heads, context, torch, gen):
+def fill_cache(ctx, heads, context, torch, gen, keep_heads=()):
+    """Fill every head with `context` tokens.  The inputs of the heads in `keep_heads`
+    are also returned as host arrays [context, len(keep_heads), DIM] (keys, values), for
+    the CPU check of the timed cache."""
     chunk = max(1, min(64, (1 << 28) // (heads * DIM)))  # <= 1 GiB per tensor
     done = 0
+    kept_k, kept_v = [], []
+    idx = torch.tensor(list(keep_heads), device="cuda", dtype=torch.long) if len(keep_heads) else None
     while done < context:
         t = min(chunk, context - done)
         k = torch.randn((t, heads, DIM), device="cuda", generator=gen)
@@ -245,8 +271,44 @@ def fill_cache(ctx, heads, context, torch, gen):
             m = torch.rand(a.shape, device="cuda", generator=gen) < 0.01
             a[m] = torch.randn(int(m.sum().item()), device="cuda", generator=gen) * 20.0
         ctx.append_all(k, v, done)
+        if idx is not None:
+            kept_k.append(k.index_select(1, idx).cpu())
+            kept_v.append(v.index_select(1, idx).cpu())
         done += t
     ctx.synchronize()
+    if idx is None:
+        return None, None
+    return torch.cat(kept_k).numpy(), torch.cat(kept_v).numpy()
+
+
+def parity_sample(ctx, sample_heads, seeds, kept_k, kept_v, steps_k, steps_v, q_dev, out_dev, n):
+    """CPU check of the cache that was just timed (outside every timed region): the sampled
+    head-instances are rebuilt on the CPU oracle from the same inputs -- the fill plus every
+    decode-step token appended since -- and compared with what the GPU holds: packed rows and
+    scales bit for bit, the last step's attention outputs within 1e-5 relative / 1e-4 absolute."""
+    import numpy as np
+    from oracle import loader
+    O = loader.oracle()
+    rows_equal, max_err, worst_excess = True, 0.0, 0.0
+    for j, h in enumerate(sample_heads):
+        hd = loader.Head(O, DIM, K_BITS, V_BITS, n, seeds[h] & (2**64 - 1))
+        hd.append_many(kept_k[:, j], kept_v[:, j])
+        for sk, sv in zip(steps_k, steps_v):
+            hd.append(sk[j], sv[j])
+        e = ctx.export_head(h)
+        live = slice(0, hd.size)
+        rows_equal &= bool((e["k_rows"][live] == hd.k_data()[live]).all() and (e["v_rows"][live] == hd.v_data()[live]).all()
+                           and (e["k_scale"][live].view(np.uint32) == hd.k_scale()[live].view(np.uint32)).all()
+                           and (e["v_scale"][live].view(np.uint32) == hd.v_scale()[live].view(np.uint32)).all()
+                           and e["ring_head"] == hd.ring_head and e["ring_size"] == hd.size)
+        want, _ = hd.compute(q_dev[h].cpu().numpy())
+        got = out_dev[h].cpu().numpy()
+        err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+        max_err = max(max_err, float(err.max()))
+        worst_excess = max(worst_excess, float((err - (1e-4 + 1e-5 * np.abs(want))).max()))
+    return {"heads": len(sample_heads), "head_indices": list(sample_heads), "tokens_per_head": n, "rows_equal": rows_equal,
+            "max_abs_err": max_err, "outputs_within_tolerance": worst_excess <= 0.0,
+            "tolerance": "1e-5 relative + 1e-4 absolute", "checker": "oracle/adaptq_oracle.c"}
 
 
 def append_bench(torch, L, peak):
@@ -327,7 +389,41 @@ def latency_bench(torch):
     return out
 
 
-def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"):
+def longctx_check(torch, dist, world, rank, ctx, keep_k, keep_v, q, o, kb, vb, N):
+    """Rank 0 rebuilds head 0 of the sharded sequence on the CPU oracle (token t came from
+    rank t mod G, local position t div G) and compares the merged output of the last step."""
+    import numpy as np
+    local = torch.stack([torch.cat(keep_k), torch.cat(keep_v)])  # [2, local_n, D] on the host
+    if dist is not None:
+        dev = local.cuda()
+        gathered = [torch.empty_like(dev) for _ in range(world)] if rank == 0 else None
+        dist.gather(dev, gathered, dst=0)
+        parts = [g.cpu() for g in gathered] if rank == 0 else None
+    else:
+        parts = [local]
+    if rank != 0:
+        return None
+    from oracle import loader
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import assert_close_conditioned, exact_attention_f64
+    full = torch.stack(parts, dim=2).reshape(2, N, DIM).numpy()  # [2, local_n, G, D] -> token t = local*G + rank
+    O = loader.oracle()
+    hd = loader.Head(O, DIM, kb, vb, N, loader.mha_head_seed(42, 0))
+    hd.append_many(full[0], full[1])
+    q0 = q[0].cpu().numpy()
+    want, _ = hd.compute(q0)
+    got = o[0, 0].cpu().numpy()
+    exact = exact_attention_f64(O, hd, q0)
+    try:
+        assert_close_conditioned(got, want, exact, "long-context head 0")
+        verdict = "ok"
+    except AssertionError as ex:
+        verdict = f"FAILED: {ex}"
+    return {"result": verdict, "max_abs_err_vs_oracle": float(np.abs(got - want).max()),
+            "oracle_abs_err_vs_float64": float(np.abs(want - exact).max()), "head": 0, "tokens": N}
+
+
+def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl", check=False):
     """Contract configuration 5: ONE sequence, 1 layer, 32 KV heads, dim 128, context
     131072, K2/V2 and K4/V4, K/V Student-t(nu=3), dense V.  Token t lives on rank
     t mod G (local ring of 131072/G tokens).  One step = one decode query per
@@ -345,6 +441,7 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
         ctx = adaptq_b200.MHAContext(H, D, kb, vb, local_n, seed=42, v_mass=0.0, hybrid_thresh=0)
         g = torch.Generator(device="cuda").manual_seed(500 + rank)
         done = 0
+        keep_k, keep_v = [], []  # head 0's inputs, for the CPU check
         while done < local_n:
             t = min(4096, local_n - done)
             kv = []
@@ -353,6 +450,9 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
                 chi = torch.randn((t, H, D, 3), device="cuda", generator=g).pow(2).mean(-1)
                 kv.append(z / torch.sqrt(chi))  # Student-t, nu = 3
             ctx.append_all(kv[0], kv[1], done)
+            if check:
+                keep_k.append(kv[0][:, 0].cpu())
+                keep_v.append(kv[1][:, 0].cpu())
             done += t
         gq = torch.Generator(device="cuda").manual_seed(77)  # the same query on every rank
         q = torch.randn((H, D), device="cuda", generator=gq)
@@ -422,8 +522,14 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
                "effective_kv_gbs_all_ranks": alg / us_total / 1e3, "local_kernel_gbs_per_gpu": alg / world / us_local / 1e3,
                "local_kernel_frac_of_peak": alg / world / us_local / 1e3 / peak,
                "algorithmic_bytes": alg, "tokens_per_rank": local_n}
+        res["exchange_share"] = max(0.0, us_total - us_local) / us_total
+        res["frac_of_peak_all_ranks"] = alg / us_total / 1e3 / (peak * world)
         if world == 1:
             res["us_per_step_compute_all"] = timed(step_single)
+        if check:
+            step_sharded()
+            torch.cuda.synchronize()
+            res["sharded_check"] = longctx_check(torch, dist, world, rank, ctx, keep_k, keep_v, q, o, kb, vb, N)
         out[f"k{kb}v{vb}"] = res
         ctx.close()
     return out
@@ -476,7 +582,9 @@ def run_ours(args):
              for hd in range(KV_HEADS)]
     ctx = adaptq_b200.MHAContext(heads, DIM, K_BITS, V_BITS, n, seeds=seeds, v_mass=0.0, hybrid_thresh=0)
     gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
-    fill_cache(ctx, heads, n, torch, gen)
+    do_parity = rank == 0 and not args.skip_parity_sample
+    sample_heads = sorted({0, heads // 3, (2 * heads) // 3 + 1, heads - 1}) if do_parity else []
+    kept_k, kept_v = fill_cache(ctx, heads, n, torch, gen, sample_heads)
 
     # device-resident inputs for `value`, pinned host inputs for `e2e`
     d_k = torch.randn((heads, DIM), device="cuda", generator=gen)
@@ -486,12 +594,16 @@ def run_ours(args):
     h_k, h_v, h_q = (t.cpu().pin_memory() for t in (d_k, d_v, d_q))
     h_o = torch.empty((heads, DIM)).pin_memory()
 
+    n_steps_done = [0]  # every step appends (d_k, d_v) once more; the CPU check replays them
+
     def step_device():
         ctx.append_all(d_k, d_v)
         ctx.compute_all(d_q, out=d_o)
+        n_steps_done[0] += 1
 
     def step_host():  # one C-ABI call: uploads, kernels and the download are pipelined inside
         ctx.decode_step(h_k, h_v, h_q, out=h_o)
+        n_steps_done[0] += 1
 
     def barrier():
         torch.cuda.synchronize()
@@ -515,6 +627,7 @@ def run_ours(args):
                 ctx.compute_all(d_q, out=d_o)
                 b.record()
                 evs.append((a, b))
+                n_steps_done[0] += 1
             else:
                 fn()
         e1.record()
@@ -542,8 +655,12 @@ def run_ours(args):
     e2e = seqs_total * args.steps / (ms_h / 1e3)
     alg_bytes = heads * (n * (DIM * K_BITS // 8 + DIM * V_BITS // 8 + 8) + 8 * DIM)
     kt = sum(kern_ms) / len(kern_ms) / 1e3
+    clk = clocks["sm_mhz"] / clocks["sm_max_mhz"] if clocks.get("sm_mhz") and clocks.get("sm_max_mhz") else None
     roof = {"bound": "hbm", "kernel": "compute_stream_kernel<K4,V2,dim128>", "achieved": alg_bytes / kt / 1e9,
             "peak": peak, "unit": "GB/s", "frac": alg_bytes / kt / 1e9 / peak, "peak_source": peak_src,
+            # the same fraction had the SM clock stayed at its maximum (kernel time x median MHz / max MHz):
+            # separates the share of the power cap from the kernel's own
+            "frac_at_max_sm_clock": (alg_bytes / (kt * clk) / 1e9 / peak) if clk else None,
             "traffic": alg_bytes * STREAM_TRAFFIC_PER_ALG_BYTE,
             "traffic_source": "ncu dram__bytes_read+write on a 1024-head launch, scaled by heads (profiles/)",
             "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kt * 1e3,
@@ -557,9 +674,30 @@ def run_ours(args):
                     "d2h_bytes_per_step": heads * DIM * 4, "ms_per_step": ms_h / args.steps, "clocks": clocks_h},
             "gpu_launches": int(launches), "roofline": roof,
             "effective_kv_gbs": alg_bytes * world / (ms / args.steps / 1e3) / 1e9}
+    if do_parity:
+        try:
+            # one more device step so that d_o belongs to the cache state the CPU replays
+            step_device()
+            ctx.synchronize()
+            hk, hv = d_k[sample_heads].cpu().numpy(), d_v[sample_heads].cpu().numpy()
+            line["parity_sample"] = parity_sample(ctx, sample_heads, seeds, kept_k, kept_v, [hk] * n_steps_done[0],
+                                                  [hv] * n_steps_done[0], d_q, d_o, n)
+        except Exception as ex:  # the headline must still print
+            line["parity_sample"] = {"error": repr(ex)}
     ctx.close()
     del ctx
     torch.cuda.empty_cache()
+    if not args.skip_longctx:
+        # the long-context configuration on the same ranks (KV range split by token; strong scaling)
+        try:
+            lres = longctx_bench(torch, dist, world, rank, args.longctx_steps, args.warmup, peak, args.exchange, check=True)
+            if rank == 0:
+                line["longctx"] = {"workload": "one sequence, 32 KV heads, dim 128, context 131072, Student-t(3), KV range "
+                                               "split by token over the ranks (BASELINE configs[4]); L2 flushed before "
+                                               "every timed step; medians; max over ranks", "scaling": "strong",
+                                   "n_gpus": world, "results": lres}
+        except Exception as ex:
+            line["longctx"] = {"error": repr(ex)}
     if rank == 0:
         if not args.skip_append_bench:
             try:
@@ -569,7 +707,7 @@ def run_ours(args):
         if not args.skip_cpu_baseline and world == 1:
             try:
                 threads = host_threads()
-                _, desc = cpu_arm(args.cpu_sample_heads or max(threads, 32), n, 4, 1, args.seqs, threads)
+                _, desc = cpu_arm(args.cpu_sample_heads or max(2 * threads, 64), n, 4, 1, args.seqs, threads)
                 line["cpu_baseline"] = desc
             except Exception as ex:
                 line["cpu_baseline"] = {"error": repr(ex)}

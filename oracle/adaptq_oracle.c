@@ -461,6 +461,16 @@ static int cmp_desc(const void *a, const void *b) {
   return (x->i > y->i) - (x->i < y->i); /* upstream std::sort leaves ties unspecified */
 }
 
+/* Hooks for the sparse-V parity tests (thread-unsafe on purpose: tests are
+ * single-threaded).  force_count >= 0 replaces the stopping rule of
+ * attention/attention.cpp:456-472 by "accumulate exactly this many rows of the
+ * sorted order"; trace_* record the running mass and the row count after every
+ * step (a block of four, or a single row) of the natural walk. */
+static int sp_force_count = -1;
+static float *sp_trace_mass = NULL;
+static int *sp_trace_count = NULL;
+static int sp_trace_cap = 0, sp_trace_len = 0;
+
 /* attention/attention.cpp:480-660.  `variant`: 0 = the path upstream takes on
  * an AVX2+FMA x86 host (compute_avx2, :373-474), 1 = its scalar 2/3/4-bit
  * fallback (:635-659).  The hybrid and K16 branches are common to both. */
@@ -666,7 +676,9 @@ int orc_head_compute_variant(const orc_head *h, const float *q, float *out,
     qsort(ord, (size_t)n, sizeof(wi_t), cmp_desc);
     float mass = 0.f;
     int ii = 0;
-    for (; ii + 3 < n && mass < h->v_mass; ii += 4) {
+    sp_trace_len = 0;
+    const int forced = sp_force_count;
+    for (; ii + 3 < n && (forced >= 0 ? ii + 3 < forced : mass < h->v_mass); ii += 4) {
       for (int t = 0; t < 4; ++t) {
         int s = slots[ord[ii + t].i];
         float e = ord[ii + t].w * h->v_scale[s] * isp;
@@ -674,14 +686,22 @@ int orc_head_compute_variant(const orc_head *h, const float *q, float *out,
         for (int j = 0; j < padded; ++j) acc[j] = fmaf(v_cb[idx[j]], e, acc[j]);
       }
       mass += ord[ii].w + ord[ii + 1].w + ord[ii + 2].w + ord[ii + 3].w;
+      if (sp_trace_mass && sp_trace_len < sp_trace_cap) {
+        sp_trace_mass[sp_trace_len] = mass;
+        sp_trace_count[sp_trace_len++] = ii + 4;
+      }
     }
-    for (; ii < n && mass < h->v_mass; ++ii) {
+    for (; ii < n && (forced >= 0 ? ii < forced : mass < h->v_mass); ++ii) {
       int s = slots[ord[ii].i];
       float w = ord[ii].w;
       float e = w * h->v_scale[s] * isp;
       row_indices(h->v_data + (size_t)s * h->v_pb, padded, h->v_bits, idx);
       for (int j = 0; j < padded; ++j) acc[j] = fmaf(v_cb[idx[j]], e, acc[j]);
       mass += w;
+      if (sp_trace_mass && sp_trace_len < sp_trace_cap) {
+        sp_trace_mass[sp_trace_len] = mass;
+        sp_trace_count[sp_trace_len++] = ii + 1;
+      }
     }
     free(ord);
   }
@@ -693,6 +713,27 @@ int orc_head_compute_variant(const orc_head *h, const float *q, float *out,
 
 int orc_head_compute(const orc_head *h, const float *q, float *out) {
   return orc_head_compute_variant(h, q, out, 0);
+}
+
+/* Sparse V with the cut moved: the first `count` rows of the weight-sorted order
+ * are accumulated (in blocks of four while four remain below `count`, then
+ * singles -- the same grouping the natural walk uses), whatever their mass.
+ * For tests that must tell a borderline cut from a wrong result. */
+int orc_head_compute_cut(const orc_head *h, const float *q, float *out, int count) {
+  sp_force_count = count < 0 ? 0 : count;
+  int n = orc_head_compute_variant(h, q, out, 0);
+  sp_force_count = -1;
+  return n;
+}
+
+/* The natural sparse-V walk of one query: running mass and accumulated row
+ * count after every step.  Returns the number of steps recorded (<= cap). */
+int orc_head_sparse_trace(const orc_head *h, const float *q, float *out, float *mass,
+                          int *count, int cap) {
+  sp_trace_mass = mass; sp_trace_count = count; sp_trace_cap = cap; sp_trace_len = 0;
+  orc_head_compute_variant(h, q, out, 0);
+  sp_trace_mass = NULL; sp_trace_count = NULL; sp_trace_cap = 0;
+  return sp_trace_len;
 }
 
 /* attention/attention.cpp:662-677 -- every query is an independent compute */

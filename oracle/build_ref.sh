@@ -2,7 +2,7 @@
 # build_ref.sh -- TEST INFRASTRUCTURE.
 #
 # Compiles the UPSTREAM AdapTQ hot-path sources where they lie (the checkout
-# named by ADAPTQ_REFERENCE_DIR, else the default below) into oracle/_ref/:
+# named by the first argument, else by ADAPTQ_REFERENCE_DIR) into oracle/_ref/:
 #
 #   libadaptq_ref.so       -O3 -ffp-contract=off   parity build (bit-exact indices)
 #   libadaptq_ref_fast.so  -O3 -mavx2 -mfma        timed CPU baseline build
@@ -19,11 +19,11 @@
 # (the patched text is never written to disk) and the script refuses to build
 # if the pre-image is not what it expects.
 set -euo pipefail
-REF="${ADAPTQ_REFERENCE_DIR:-/root/reference}"
+REF="${1:-${ADAPTQ_REFERENCE_DIR:-}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
-if [ ! -f "$REF/attention/attention.cpp" ]; then
-  echo "build_ref.sh: no upstream sources at $REF; keeping any prebuilt oracle/_ref" >&2
+if [ -z "$REF" ] || [ ! -f "$REF/attention/attention.cpp" ]; then
+  echo "build_ref.sh: no upstream checkout given (argument or ADAPTQ_REFERENCE_DIR); keeping any prebuilt oracle/_ref" >&2
   exit 0
 fi
 mkdir -p "$OUT"

@@ -80,6 +80,12 @@ class _Lib:
         self.unpack_indices = g("unpack_indices"); self.unpack_indices.argtypes = [_u8p, C.c_int, C.c_int, _u8p]; self.unpack_indices.restype = C.c_int
         self.codebook = g("codebook"); self.codebook.argtypes = [C.c_int]; self.codebook.restype = _f32p
         self.codebook_size = g("codebook_size"); self.codebook_size.argtypes = [C.c_int]; self.codebook_size.restype = C.c_int
+        if prefix == "orc_":  # test hooks that only the restatement has
+            self.head_compute_cut = g("head_compute_cut")
+            self.head_compute_cut.argtypes = [C.c_void_p, _f32p, _f32p, C.c_int]; self.head_compute_cut.restype = C.c_int
+            self.head_sparse_trace = g("head_sparse_trace")
+            self.head_sparse_trace.argtypes = [C.c_void_p, _f32p, _f32p, _f32p, C.POINTER(C.c_int), C.c_int]
+            self.head_sparse_trace.restype = C.c_int
 
     # -- numpy conveniences -------------------------------------------------
     def signs(self, n: int, seed: int) -> np.ndarray:
@@ -152,6 +158,25 @@ class Head:
         out = np.zeros(self.dim, dtype=np.float32)
         n = self.L.head_compute(self.h, _ptr(q, _f32p), _ptr(out, _f32p))
         return out, n
+
+    def compute_cut(self, q, count):
+        """Sparse V with exactly `count` rows of the sorted order accumulated (oracle only)."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        out = np.zeros(self.dim, dtype=np.float32)
+        self.L.head_compute_cut(self.h, _ptr(q, _f32p), _ptr(out, _f32p), int(count))
+        return out
+
+    def sparse_trace(self, q):
+        """(output, running mass after every step, rows accumulated after every step) of the
+        natural sparse-V walk (oracle only)."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        out = np.zeros(self.dim, dtype=np.float32)
+        cap = self.size + 4
+        mass = np.zeros(cap, dtype=np.float32)
+        count = np.zeros(cap, dtype=np.int32)
+        n = self.L.head_sparse_trace(self.h, _ptr(q, _f32p), _ptr(out, _f32p), _ptr(mass, _f32p),
+                                     count.ctypes.data_as(C.POINTER(C.c_int)), cap)
+        return out, mass[:n].copy(), count[:n].copy()
 
     def compute_batch(self, qs):
         qs = np.ascontiguousarray(qs, dtype=np.float32)

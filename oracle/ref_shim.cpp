@@ -107,9 +107,11 @@ int ref_max_threads(void) {
 
 // Timing harness: `n_heads` independent heads (one worker per head, handles
 // are independent), each appended with `n_tokens` tokens from keys/vals
-// [n_heads][n_tokens][dim] and then queried `n_steps` times with
-// queries[n_heads][dim].  Returns seconds for the append phase in *t_append
-// and for the compute phase in *t_compute.  outs is [n_heads][dim] (last step).
+// [n_heads][n_tokens][dim]; then `n_steps` decode steps, each one append of one
+// more token per head (row step % n_tokens again; with capacity == n_tokens the
+// ring is full and evicts) followed by one query per head from
+// queries[n_heads][dim].  Returns seconds for the fill in *t_append and for the
+// decode steps in *t_compute.  outs is [n_heads][dim] (last step).
 int ref_time_heads(int n_heads, int dim, int k_bits, int v_bits, int capacity,
                    uint64_t base_seed, float v_mass, int hybrid_thresh,
                    const float *keys, const float *vals, int n_tokens,
@@ -138,8 +140,11 @@ int ref_time_heads(int n_heads, int dim, int k_bits, int v_bits, int capacity,
   auto t1 = std::chrono::steady_clock::now();
   for (int s = 0; s < n_steps; ++s) {
 #pragma omp parallel for schedule(dynamic, 1) num_threads(n_threads)
-    for (int i = 0; i < n_heads; ++i)
+    for (int i = 0; i < n_heads; ++i) {
+      const size_t row = ((size_t)i * n_tokens + (size_t)(s % n_tokens)) * dim;
+      heads[i]->append_kv(keys + row, vals + row, n_tokens + s);
       heads[i]->compute(queries + (size_t)i * dim, outs + (size_t)i * dim);
+    }
   }
   auto t2 = std::chrono::steady_clock::now();
   *t_append = std::chrono::duration<double>(t1 - t0).count();

@@ -51,49 +51,130 @@ def test_compute_matches_oracle(gpu_lib, orc, dim, kb, vb, cap, T, vm, hyb, dist
     ctx.synchronize()
 
 
-def sparse_cut(weights, v_mass):
-    """Number of rows upstream accumulates (attention.cpp:455-472) and the mass it stops at."""
-    w = np.sort(weights.astype(np.float32))[::-1]
-    mass, ii, n = np.float32(0), 0, len(w)
-    while ii + 3 < n and mass < v_mass:
-        mass = np.float32(mass + np.float32(np.float32(np.float32(w[ii] + w[ii + 1]) + w[ii + 2]) + w[ii + 3]))
-        ii += 4
-    while ii < n and mass < v_mass:
-        mass = np.float32(mass + w[ii])
-        ii += 1
-    return ii, float(mass)
-
-
-@pytest.mark.parametrize("dim,kb,vb,T,vm", [(64, 4, 2, 2048, 0.95), (128, 4, 4, 700, 0.7), (64, 3, 2, 333, 0.5),
-                                            # 4096- and 8192-token block sorts, and the device-wide sort beyond
-                                            (128, 4, 2, 3000, 0.9), (64, 2, 2, 6000, 0.95), (64, 4, 2, 9000, 0.9)])
-def test_sparse_v_matches_oracle(gpu_lib, orc, dim, kb, vb, T, vm):
-    """Engine defaults past the hybrid window (the reference's own CPU-runnable configuration as it ships).  The cut
-    is found in blocks of four rows, so a query whose running mass lands within
-    rounding distance of v_mass may legitimately stop one block earlier or later;
-    such borderline queries are skipped, every other one must match."""
+@pytest.mark.parametrize("dim,kb,vb,T,cap,vm", [(64, 4, 2, 2048, 2048, 0.95), (128, 4, 4, 700, 700, 0.7), (64, 3, 2, 333, 333, 0.5),
+                                                # 4096- and 8192-token block sorts, and the device-wide sort beyond
+                                                (128, 4, 2, 3000, 3000, 0.9), (64, 2, 2, 6000, 6000, 0.95), (64, 4, 2, 9000, 9000, 0.9),
+                                                # wrapped rings: the sort runs over logical (oldest-first) positions
+                                                (64, 4, 2, 1500, 1024, 0.95), (128, 2, 2, 12000, 9000, 0.9)])
+def test_sparse_v_matches_oracle(gpu_lib, orc, dim, kb, vb, T, cap, vm):
+    """Engine defaults past the hybrid window (the reference's own CPU-runnable configuration as it
+    ships).  Every (query, head) must match the oracle within the normal tolerance, except where the
+    cut is provably borderline: the oracle's running mass at the neighbouring step boundary lies
+    within rounding distance of v_mass AND the output equals the oracle's with the cut moved there
+    (helpers.assert_sparse_close).  Most queries must match outright."""
     from adaptq_b200 import MHAContext
+    from helpers import assert_sparse_close
     heads = 4
     rng = np.random.default_rng(T)
     k, v = make_kv(rng, T, heads, dim)
-    ctx = MHAContext(heads, dim, kb, vb, T, seed=42, v_mass=vm, hybrid_thresh=0)
-    cpu = CpuHeads(orc, heads, dim, kb, vb, T, 42, vm, 0)
-    dense = CpuHeads(orc, heads, dim, kb, vb, T, 42, 0.0, 0)
+    ctx = MHAContext(heads, dim, kb, vb, cap, seed=42, v_mass=vm, hybrid_thresh=0)
+    cpu = CpuHeads(orc, heads, dim, kb, vb, cap, 42, vm, 0)
     ctx.append_all(k, v)
     cpu.append_many(k, v)
-    dense.append_many(k, v)
-    checked = 0
+    plain = 0
     for i in range(8):
         q = rng.standard_normal((heads, dim)).astype(np.float32)
-        got, want = ctx.compute_all(q), cpu.compute(q)
+        got = ctx.compute_all(q)
         for h in range(heads):
-            if abs(np.abs(got[h] - want[h]).max()) <= 1e-4:
-                checked += 1
-                continue
-            # disagreement is only acceptable if the dense answer is far away too
-            # (i.e. it is a cut-position effect) and the cut is borderline
-            assert_close(got[h], want[h], f"query {i} head {h}", atol=2e-3)
-    assert checked >= 8 * heads * 0.9
+            plain += bool(assert_sparse_close(got[h], cpu.heads[h], q[h], vm, f"query {i} head {h}"))
+    assert plain >= 8 * heads * 0.9, f"only {plain} of {8 * heads} queries matched without moving the cut"
+
+
+def test_sparse_v_ties_follow_logical_order(gpu_lib, orc):
+    """Equal weights: the same (key, value) pairs appended several times so that whole
+    groups of tokens tie exactly, on a wrapped ring.  The oracle breaks ties by logical
+    position (oldest first); so does the CUDA path, hence equal outputs although the
+    values of tied tokens differ."""
+    from adaptq_b200 import MHAContext
+    from helpers import assert_sparse_close
+    heads, dim, cap = 2, 64, 96
+    rng = np.random.default_rng(4)
+    base_k, _ = make_kv(rng, 8, heads, dim)
+    k = np.concatenate([base_k] * 20)              # 160 tokens, every key 20 times
+    v = rng.standard_normal(k.shape).astype(np.float32)  # but different values
+    ctx = MHAContext(heads, dim, 4, 2, cap, seed=1, v_mass=0.6, hybrid_thresh=0)
+    cpu = CpuHeads(orc, heads, dim, 4, 2, cap, 1, 0.6, 0)
+    ctx.append_all(k, v)
+    cpu.append_many(k, v)
+    for i in range(4):
+        q = rng.standard_normal((heads, dim)).astype(np.float32)
+        got = ctx.compute_all(q)
+        for h in range(heads):
+            assert_sparse_close(got[h], cpu.heads[h], q[h], 0.6, f"query {i} head {h}")
+
+
+# K rows that make logits NaN / +-inf / hugely negative, V rows with infinite scales.
+# (upstream tests that such appends do not crash: tests/unit/test_api.cpp:334-358)
+def _special_rows(dim):
+    nan = np.full(dim, np.nan, np.float32)
+    big = np.full(dim, 1e38, np.float32)
+    zero = np.zeros(dim, np.float32)
+    return {"nan": nan, "big": big, "negbig": -big, "zero": zero}
+
+
+def _assert_same_or_both_nonfinite(got, want, what):
+    got, want = np.asarray(got, np.float32), np.asarray(want, np.float32)
+    fin = np.isfinite(want)
+    assert (np.isfinite(got) == fin).all(), f"{what}: finite pattern differs: got {got[:6]} want {want[:6]}"
+    if fin.any():
+        assert_close(got[fin], want[fin], what)
+
+
+@pytest.mark.parametrize("dim,kb,vb,T,where", [
+    (128, 4, 2, 600, "k"), (128, 4, 2, 600, "v"),       # streaming kernel, one span
+    (128, 4, 2, 20000, "k"), (128, 2, 2, 20000, "v"),   # several spans, merged inside the launch
+    (64, 3, 2, 900, "k"), (64, 4, 2, 900, "v"),         # general kernel, spans merged by the last block
+    (64, 16, 2, 300, "k"), (64, 16, 16, 300, "v"),      # FP32 rows
+])
+@pytest.mark.parametrize("kind", ["zero", "nan", "big", "negbig"])
+def test_special_value_rows_behave_like_upstream(gpu_lib, orc, dim, kb, vb, T, where, kind):
+    """A cache that holds a zero, NaN or 1e38 row.  Upstream's attention has no guard on
+    these paths (attention/attention.cpp:422-429, :578-582), so a NaN or +inf logit makes
+    the whole output NaN, a -inf logit weighs nothing, an infinite V scale gives inf or
+    NaN.  The CUDA path must give the oracle's numbers where they are finite and a
+    non-finite value wherever the oracle's is non-finite -- also when the poisoned
+    row sits in one of several spans."""
+    from adaptq_b200 import MHAContext
+    if (kb if where == "k" else vb) == 16 and kind in ("big", "negbig"):
+        pytest.skip("sums of raw 1e38 values overflow or not depending on the order of the additions")
+    heads = 2
+    rng = np.random.default_rng(17)
+    k, v = make_kv(rng, T, heads, dim)
+    row = _special_rows(dim)[kind]
+    (k if where == "k" else v)[T // 3, 1] = row          # head 1 gets the special row, head 0 stays clean
+    ctx = MHAContext(heads, dim, kb, vb, T, seed=6, v_mass=0.0, hybrid_thresh=0)
+    cpu = CpuHeads(orc, heads, dim, kb, vb, T, 6)
+    ctx.append_all(k, v)
+    cpu.append_many(k, v)
+    for i in range(2):
+        q = rng.standard_normal((heads, dim)).astype(np.float32)
+        got, want = ctx.compute_all(q), cpu.compute(q)
+        assert np.isfinite(want[0]).all()
+        for h in range(heads):
+            _assert_same_or_both_nonfinite(got[h], want[h], f"{kind} in {where}, query {i} head {h}")
+    ctx.synchronize()
+
+
+@pytest.mark.parametrize("kind", ["negbig_all", "nan_one"])
+def test_hybrid_window_sum_guard(gpu_lib, orc, kind):
+    """The FP32 window is the one branch with a guard (attention/attention.cpp:513): a sum of
+    exponentials that is zero or not finite is replaced by n.  All logits at -inf -> zeros."""
+    from adaptq_b200 import MHAContext
+    heads, dim, T = 2, 64, 40
+    rng = np.random.default_rng(2)
+    k, v = make_kv(rng, T, heads, dim)
+    if kind == "negbig_all":
+        k[:, 1, :] = -3e37       # q = +1 everywhere -> every dot product overflows to -inf
+    else:
+        k[5, 1, :] = np.nan
+    ctx = MHAContext(heads, dim, 4, 2, 64, seed=6, v_mass=0.95, hybrid_thresh=512)
+    cpu = CpuHeads(orc, heads, dim, 4, 2, 64, 6, 0.95, 512)
+    ctx.append_all(k, v)
+    cpu.append_many(k, v)
+    q = np.ones((heads, dim), np.float32)
+    got, want = ctx.compute_all(q), cpu.compute(q)
+    for h in range(heads):
+        _assert_same_or_both_nonfinite(got[h], want[h], f"{kind} head {h}")
 
 
 def test_compute_batch_and_single_head_calls(gpu_lib, orc):

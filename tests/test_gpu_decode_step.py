@@ -34,11 +34,14 @@ def test_decode_step_small_against_oracle(gpu_lib, orc):
 
 
 @pytest.mark.parametrize("bits", [(4, 2), (2, 4)])
-def test_decode_step_pipelined_equals_two_calls(gpu_lib, bits):
+def test_decode_step_pipelined_equals_two_calls(gpu_lib, orc, bits):
     import torch
     import adaptq_b200
+    from oracle import loader
     heads, dim, cap = 4096 + 40, 128, 96  # not a multiple of the chunk count
     kb, vb = bits
+    sample = (0, 517, heads - 1)          # these heads are also run on the CPU oracle
+    cpu = {h: loader.Head(orc, dim, kb, vb, cap, loader.mha_head_seed(5, h)) for h in sample}
     g = torch.Generator(device="cuda").manual_seed(11)
     a = adaptq_b200.MHAContext(heads, dim, kb, vb, cap, seed=5, v_mass=0.0, hybrid_thresh=0)
     b = adaptq_b200.MHAContext(heads, dim, kb, vb, cap, seed=5, v_mass=0.0, hybrid_thresh=0)
@@ -46,6 +49,8 @@ def test_decode_step_pipelined_equals_two_calls(gpu_lib, bits):
     pre_v = torch.randn((cap - 2, heads, dim), device="cuda", generator=g)
     a.append_all(pre_k, pre_v)
     b.append_all(pre_k, pre_v)
+    for h, hd in cpu.items():
+        hd.append_many(pre_k[:, h].cpu().numpy(), pre_v[:, h].cpu().numpy())
     launches0 = gpu_lib.adaptq_kernel_launches()
     for step in range(4):  # the last two steps evict
         k = torch.randn((heads, dim), device="cuda", generator=g)
@@ -57,8 +62,12 @@ def test_decode_step_pipelined_equals_two_calls(gpu_lib, bits):
         b.append_all(k, v)
         want = b.compute_all(q)
         assert torch.equal(got, want.cpu()), f"step {step}: pipelined decode step differs from append + compute"
+        for h, hd in cpu.items():
+            hd.append(k[h].cpu().numpy(), v[h].cpu().numpy())
+            assert_close(got[h].numpy(), hd.compute(q[h].cpu().numpy())[0], f"step {step} head {h} against the oracle")
     assert gpu_lib.adaptq_kernel_launches() > launches0
-    for h in (0, 517, heads - 1):
+    for h in sample:
+        assert_cache_equal(a.export_head(h), cpu[h], f"head {h} against the oracle")
         ea, eb = a.export_head(h), b.export_head(h)
         for key in ("k_rows", "v_rows", "k_scale", "v_scale"):
             assert np.array_equal(ea[key], eb[key]), (h, key)

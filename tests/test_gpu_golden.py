@@ -6,7 +6,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import assert_close
+from helpers import CpuHeads, assert_close, assert_sparse_close
 
 pytestmark = pytest.mark.gpu
 
@@ -15,7 +15,7 @@ FILES = sorted(f for f in glob.glob(os.path.join(os.path.dirname(__file__), "gol
 
 
 @pytest.mark.parametrize("path", FILES, ids=[os.path.basename(f)[:-4] for f in FILES])
-def test_cuda_reproduces_golden(gpu_lib, path):
+def test_cuda_reproduces_golden(gpu_lib, orc, path):
     from adaptq_b200 import MHAContext
     g = np.load(path)
     dim, heads = int(g["dim"]), int(g["heads"])
@@ -32,7 +32,22 @@ def test_cuda_reproduces_golden(gpu_lib, path):
         assert (e["k_scale"][live].view(np.uint32) == g[f"k_scale_{h}"][live].view(np.uint32)).all()
         assert (e["v_scale"][live].view(np.uint32) == g[f"v_scale_{h}"][live].view(np.uint32)).all()
         assert (e["signs"] == g[f"signs_{h}"]).all()
-    sparse = float(g["v_mass"]) > 0 and int(g[f"ring_0"][2]) != int(g[f"ring_0"][1])
+    # sparse V is active when v_mass > 0 and the FP32 window no longer covers the cache
+    sparse = float(g["v_mass"]) > 0 and int(g[f"ring_0"][2]) != int(g[f"ring_0"][1]) and int(g["k_bits"]) != 16
+    cpu = None
+    if sparse:  # a borderline cut may stop one step earlier or later: the oracle tells which (helpers.assert_sparse_close)
+        cpu = CpuHeads(orc, heads, dim, int(g["k_bits"]), int(g["v_bits"]), int(g["capacity"]), int(g["base_seed"]),
+                       float(g["v_mass"]), int(g["hybrid_thresh"]))
+        cpu.append_many(g["keys"], g["vals"])
     for i in range(g["queries"].shape[0]):
         got = ctx.compute_all(g["queries"][i])
-        assert_close(got, g["outs"][i], f"query {i}", atol=2e-3 if sparse else 1e-4)
+        if not sparse:
+            assert_close(got, g["outs"][i], f"query {i}")
+            continue
+        for h in range(heads):
+            try:
+                assert_close(got[h], g["outs"][i][h], f"query {i} head {h}")
+            except AssertionError:
+                # the fixture (upstream's output) and the oracle agree bit for bit on the CPU
+                # (tests/test_golden.py), so the oracle may arbitrate the cut
+                assert_sparse_close(got[h], cpu.heads[h], g["queries"][i][h], float(g["v_mass"]), f"query {i} head {h}")

@@ -21,7 +21,8 @@ from helpers import ATOL, RTOL
 pytestmark = pytest.mark.gpu
 
 
-def _ctx(heads, dim, kb, vb, T, seed, torch):
+def _ctx(heads, dim, kb, vb, T, seed, torch, cpu=None):
+    """A filled cache; `cpu` (CPU-checker heads) receives the same tokens."""
     from adaptq_b200 import MHAContext
     ctx = MHAContext(heads, dim, kb, vb, T, seed=seed, v_mass=0.0, hybrid_thresh=0)
     g = torch.Generator(device="cuda").manual_seed(seed)
@@ -31,15 +32,20 @@ def _ctx(heads, dim, kb, vb, T, seed, torch):
         k = torch.randn((t, heads, dim), device="cuda", generator=g)
         v = torch.randn((t, heads, dim), device="cuda", generator=g)
         ctx.append_all(k, v)
+        if cpu is not None:
+            cpu.append_many(k.cpu().numpy(), v.cpu().numpy())
         done += t
     return ctx, g
 
 
-def test_static_scratch_matches_regular_entry_point_twice(gpu_lib):
+def test_static_scratch_matches_regular_entry_point_twice(gpu_lib, orc):
     import torch
+    from helpers import CpuHeads, assert_close
+    from adaptq_b200 import _lib
     L = gpu_lib
     heads, dim, T = 3, 128, 20000          # 20 000 tokens -> several spans -> the scratch is really used
-    ctx, g = _ctx(heads, dim, 4, 2, T, 11, torch)
+    cpu = CpuHeads(orc, heads, dim, 4, 2, T, 11)
+    ctx, g = _ctx(heads, dim, 4, 2, T, 11, torch, cpu)
     other, _ = _ctx(2, 128, 2, 2, 9000, 12, torch)   # a second handle sharing the same static array
     for round_ in range(2):
         q = torch.randn((heads, 2, dim), device="cuda", generator=g)
@@ -47,14 +53,21 @@ def test_static_scratch_matches_regular_entry_point_twice(gpu_lib):
         got = torch.full_like(q, float("nan"))
         assert L.adaptq_mha_compute_all(ctx._h, C.c_void_p(q.data_ptr()), 2, C.c_void_p(want.data_ptr())) == T
         mem_before = torch.cuda.mem_get_info()[0]
+        info = _lib.MhaInfo()
+        L.adaptq_mha_info(ctx._h, C.byref(info))
+        bytes_before = info.device_bytes     # everything the handle has allocated, staging included
         n = L.adaptq_mha_compute_all_static(ctx._h, C.c_void_p(q.data_ptr()), 2, C.c_void_p(got.data_ptr()))
         assert n == T, L.adaptq_last_error().decode()
         torch.cuda.synchronize()
+        L.adaptq_mha_info(ctx._h, C.byref(info))
+        assert info.device_bytes == bytes_before, "the allocation-free entry point grew one of the handle's buffers"
         if round_ == 1:  # the address lookup of the very first call is behind us: nothing may be allocated
             assert torch.cuda.mem_get_info()[0] >= mem_before
         a, b = got.cpu().numpy(), want.cpu().numpy()
         assert np.isfinite(a).all()
         assert (np.abs(a - b) <= ATOL + RTOL * np.abs(b)).all(), f"round {round_}: max |diff| {np.abs(a - b).max()}"
+        # ... and both are what the CPU oracle computes from the same tokens
+        assert_close(a, cpu.compute_batch(q.cpu().numpy()), f"round {round_} against the oracle")
         # dirty the shared array through another handle before the next round
         q2 = torch.randn((2, 1, 128), device="cuda", generator=g)
         o2, w2 = torch.empty_like(q2), torch.empty_like(q2)

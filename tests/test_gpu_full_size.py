@@ -31,12 +31,16 @@ def test_full_ring_8192_with_eviction_every_step(gpu_lib, orc):
     q = rng.standard_normal((cap + extra, heads, dim)).astype(np.float32)
     ctx = MHAContext(heads, dim, 4, 2, cap, seed=42, v_mass=0.0, hybrid_thresh=0)
     cpu = CpuHeads(orc, heads, dim, 4, 2, cap, 42)
-    check_at = set(range(cap - 2, cap + extra)) | {0, 1, 63, 64, 1000, 4095, 4096}
+    check_at = set(range(cap - 2, cap + 6)) | set(range(cap + 6, cap + extra, 5)) | {0, 1, 63, 64, 1000, 4095, 4096, cap + extra - 1}
     for t in range(cap + extra):          # single-token decode steps all the way: fill, then evict every step
         out = ctx.decode_step(k[t], v[t], q[t], pos=t)
         cpu.append_many(k[t:t + 1], v[t:t + 1])
         if t in check_at:
-            assert_close(out, cpu.compute(q[t]), f"step {t}")
+            # 1 % N(0,20) entries: a few tokens carry most of the mass and outputs reach the tens, where
+            # the FP32 reference is itself a few 1e-4 from the float64 value of its own formula
+            want = cpu.compute(q[t])
+            exact = np.stack([exact_attention_f64(orc, cpu.heads[h], q[t, h]) for h in range(heads)])
+            assert_close_conditioned(out, want, exact, f"step {t}")
     for h in range(heads):
         e = ctx.export_head(h)
         assert e["ring_size"] == cap and e["ring_head"] == extra % cap

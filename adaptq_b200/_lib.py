@@ -24,7 +24,7 @@ class MhaInfo(C.Structure):
                 ("v_mass", C.c_float), ("device_bytes", C.c_size_t)]
 
 
-# name -> (restype, argtypes); every symbol declared in include/adaptq.h and include/adaptq_b200.h
+# name -> (restype, argtypes); every symbol declared in include/*.h
 SYMBOLS = {
     "adaptq_last_error": (C.c_char_p, []),
     "adaptq_create": (C.c_void_p, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_float, C.c_int]),
@@ -59,6 +59,25 @@ SYMBOLS = {
     "adaptq_mha_info": (C.c_int, [C.c_void_p, C.POINTER(MhaInfo)]),
     "adaptq_mha_export_head": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_void_p, intp, intp, intp]),
+    # include/adaptq_runtime.h
+    "adaptq_runtime_create": (C.c_void_p, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
+    "adaptq_runtime_destroy": (None, [C.c_void_p]),
+    "adaptq_runtime_append": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "adaptq_runtime_compute": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "adaptq_runtime_append_token": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "adaptq_runtime_compute_token": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "adaptq_runtime_reset": (C.c_int, [C.c_void_p]),
+    "adaptq_runtime_token_pos": (C.c_int, [C.c_void_p]),
+    "adaptq_runtime_handle": (C.c_void_p, [C.c_void_p]),
+    "adaptq_runtime_snapshot_save": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "adaptq_runtime_snapshot_load": (C.c_void_p, [C.c_char_p, C.c_int, C.c_float]),
+    "adaptq_mha_import_head": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int, C.c_int, C.c_int]),
+    "adaptq_kernel_fwht_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "adaptq_kernel_fwht_inverse": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "adaptq_kernel_kdot_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "adaptq_kernel_vaccum_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "adaptq_kernel_backend_name": (C.c_char_p, []),
     "adaptq_kernel_launches": (C.c_ulonglong, []),
     "adaptq_set_kernel_policy": (C.c_int, [C.c_int]),
 }

@@ -5,10 +5,12 @@
 // this directory.  There is no CPU compute path: if no CUDA device is usable
 // every constructor fails with an error string.
 #include "../../include/adaptq_b200.h"
+#include "../../include/adaptq_runtime.h"
 #include "append.cuh"
 #include "compute_general.cuh"
 #include "compute_sparse.cuh"
 #include "compute_stream.cuh"
+#include "runtime_v2.cuh"
 
 #include <algorithm>
 #include <atomic>
@@ -197,6 +199,7 @@ Group *create_group(const char *fn, const char *bad_args_msg, int n_heads, const
   c.log2p = 0; while ((1 << c.log2p) < P) ++c.log2p;
   c.k_row = row_bytes(P, k_bits); c.v_row = row_bytes(P, v_bits);
   c.cap = capacity; c.hyb = hyb; c.v_mass = v_mass;
+  c.sparse_block = 4;
   // +128 slack: bulk copies of the last tile round their size up to 16 bytes
   c.k_stride = round_up((size_t)capacity * c.k_row, 128) + 128;
   c.v_stride = round_up((size_t)capacity * c.v_row, 128) + 128;
@@ -1398,3 +1401,5 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
 
 
 } // extern "C"
+
+#include "runtime_v2_host.inc"

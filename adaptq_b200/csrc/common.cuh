@@ -63,6 +63,10 @@ struct CacheView {
   int s_stride, sign_words;
   int n_heads, dim, padded, log2p, k_bits, v_bits, k_row, v_row, cap, hyb;
   float v_mass;
+  // Sparse V walks the sorted weights in blocks of this many rows while a whole block
+  // remains (4: AttentionHead, attention.cpp:456-465), then row by row; 1 = row by row
+  // from the start (HARFixedStrategy::compute_full, strategies/har_fixed.cpp:258-264).
+  int sparse_block;
 };
 
 __host__ __device__ inline int row_bytes(int padded, int bits) {

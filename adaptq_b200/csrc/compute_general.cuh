@@ -505,8 +505,9 @@ __global__ void __launch_bounds__(CG_THREADS) sparse_accumulate_kernel(
   if (tid == 0) {
     float mass = 0.f;
     int ii = 0;
-    for (; ii + 3 < n && mass < c.v_mass; ii += 4)
-      mass = __fadd_rn(mass, __fadd_rn(__fadd_rn(__fadd_rn(w[ii], w[ii + 1]), w[ii + 2]), w[ii + 3]));
+    if (c.sparse_block == 4)
+      for (; ii + 3 < n && mass < c.v_mass; ii += 4)
+        mass = __fadd_rn(mass, __fadd_rn(__fadd_rn(__fadd_rn(w[ii], w[ii + 1]), w[ii + 2]), w[ii + 3]));
     for (; ii < n && mass < c.v_mass; ++ii) mass = __fadd_rn(mass, w[ii]);
     s_count = ii;
   }

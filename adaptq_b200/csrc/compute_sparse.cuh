@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   if (tid == 0) {
     float mass = 0.f;
     int ii = 0;
-    for (; ii + 3 < n && mass < c.v_mass; ii += 4) mass = __fadd_rn(mass, bsum[ii >> 2]);
+    if (c.sparse_block == 4)
+      for (; ii + 3 < n && mass < c.v_mass; ii += 4) mass = __fadd_rn(mass, bsum[ii >> 2]);
     for (; ii < n && mass < c.v_mass; ++ii) mass = __fadd_rn(mass, s_w[ii]);
     s_count = ii;
   }

@@ -332,6 +332,10 @@ typedef struct orc_head {
   /* hybrid FP32 mirror, include/attention.h:20 */
   float *raw_kv;
   size_t raw_len, raw_cap;
+  /* Sparse-V walk: 4 = blocks of four rows, then single rows (attention/attention.cpp:456-472);
+   * 1 = single rows from the start, the rule of upstream's second stack
+   * (HARFixedStrategy::compute_full, strategies/har_fixed.cpp:258-264). */
+  int sparse_block;
 } orc_head;
 
 static int packed_bytes(int padded, int bits) { /* cache/ring_buffer.cpp:52-53 */
@@ -358,6 +362,7 @@ orc_head *orc_head_create(int dim, int k_bits, int v_bits, int capacity,
   int padded = orc_next_pow2(dim);
   if (padded > ORC_MAX_PADDED) return NULL;
   orc_head *h = (orc_head *)calloc(1, sizeof(orc_head));
+  if (h) h->sparse_block = 4;
   if (!h) return NULL;
   h->dim = dim; h->padded = padded; h->k_bits = k_bits; h->v_bits = v_bits;
   h->capacity = capacity; h->hybrid_thresh = hybrid_thresh; h->v_mass = v_mass;
@@ -678,7 +683,7 @@ int orc_head_compute_variant(const orc_head *h, const float *q, float *out,
     int ii = 0;
     sp_trace_len = 0;
     const int forced = sp_force_count;
-    for (; ii + 3 < n && (forced >= 0 ? ii + 3 < forced : mass < h->v_mass); ii += 4) {
+    for (; h->sparse_block == 4 && ii + 3 < n && (forced >= 0 ? ii + 3 < forced : mass < h->v_mass); ii += 4) {
       for (int t = 0; t < 4; ++t) {
         int s = slots[ord[ii + t].i];
         float e = ord[ii + t].w * h->v_scale[s] * isp;
@@ -714,6 +719,8 @@ int orc_head_compute_variant(const orc_head *h, const float *q, float *out,
 int orc_head_compute(const orc_head *h, const float *q, float *out) {
   return orc_head_compute_variant(h, q, out, 0);
 }
+
+void orc_head_set_sparse_block(orc_head *h, int rows) { h->sparse_block = rows == 1 ? 1 : 4; }
 
 /* Sparse V with the cut moved: the first `count` rows of the weight-sorted order
  * are accumulated (in blocks of four while four remain below `count`, then

@@ -6,6 +6,8 @@
 #
 #   libadaptq_ref.so       -O3 -ffp-contract=off   parity build (bit-exact indices)
 #   libadaptq_ref_fast.so  -O3 -mavx2 -mfma        timed CPU baseline build
+#   libadaptq_ref_v2.so    -O3 -ffp-contract=off   upstream's second stack (RuntimeContext,
+#                          SessionSnapshot, IKernelBackend) behind ref_v2_shim.cpp
 #
 # Nothing from upstream is copied into this repository; only object code lands
 # in the git-ignored oracle/_ref/.  Upstream's own build system is not used.
@@ -56,4 +58,20 @@ build_one() {  # $1 = output name, rest = flags
 
 build_one libadaptq_ref.so -O3 -ffp-contract=off
 build_one libadaptq_ref_fast.so -O3 -mavx2 -mfma
-echo "built $OUT/libadaptq_ref.so and $OUT/libadaptq_ref_fast.so"
+
+# Upstream's second stack.  Its strategies and storages are header-style sources that
+# runtime/runtime_context.cpp includes itself (one translation unit, as upstream's own
+# build does it), so only the files below are compiled; the AVX2 kernel file gets the
+# machine flags upstream's build gives it.
+V2_SRCS=(core/fwht.cpp core/codebook.cpp core/quantizer.cpp core/cost_optimizer.cpp core/quality_oracle.cpp
+         kernels/scalar/kdot_scalar.cpp kernels/kernel_selector.cpp runtime/runtime_context.cpp
+         replay/session_snapshot.cpp replay/replay_engine.cpp)
+tmp="$(mktemp -d)"
+for s in "${V2_SRCS[@]}"; do
+  g++ -std=c++17 -fPIC -O3 -ffp-contract=off "${INC[@]}" -c "$REF/$s" -o "$tmp/$(basename "$s" .cpp).o"
+done
+g++ -std=c++17 -fPIC -O3 -mavx2 -mfma "${INC[@]}" -c "$REF/kernels/avx2/kdot_avx2.cpp" -o "$tmp/kdot_avx2.o"
+g++ -std=c++17 -fPIC -O3 -ffp-contract=off "${INC[@]}" -c "$HERE/ref_v2_shim.cpp" -o "$tmp/ref_v2_shim.o"
+g++ -shared -o "$OUT/libadaptq_ref_v2.so" "$tmp"/*.o
+rm -f "$tmp"/*.o; rmdir "$tmp"
+echo "built $OUT/libadaptq_ref.so, $OUT/libadaptq_ref_fast.so and $OUT/libadaptq_ref_v2.so"

@@ -86,6 +86,8 @@ class _Lib:
             self.head_sparse_trace = g("head_sparse_trace")
             self.head_sparse_trace.argtypes = [C.c_void_p, _f32p, _f32p, _f32p, C.POINTER(C.c_int), C.c_int]
             self.head_sparse_trace.restype = C.c_int
+            self.head_set_sparse_block = g("head_set_sparse_block")
+            self.head_set_sparse_block.argtypes = [C.c_void_p, C.c_int]; self.head_set_sparse_block.restype = None
 
     # -- numpy conveniences -------------------------------------------------
     def signs(self, n: int, seed: int) -> np.ndarray:
@@ -158,6 +160,10 @@ class Head:
         out = np.zeros(self.dim, dtype=np.float32)
         n = self.L.head_compute(self.h, _ptr(q, _f32p), _ptr(out, _f32p))
         return out, n
+
+    def set_sparse_block(self, rows):
+        """1: sparse V adds single rows from the start (the V2 stack's rule); 4: blocks of four first."""
+        self.L.head_set_sparse_block(self.h, rows)
 
     def compute_cut(self, q, count):
         """Sparse V with exactly `count` rows of the sorted order accumulated (oracle only)."""
@@ -262,3 +268,114 @@ def ref_max_threads() -> int:
     L = reference(True).lib
     L.ref_max_threads.restype = C.c_int
     return L.ref_max_threads()
+
+
+class RefV2:
+    """Upstream's second stack (RuntimeContext / SessionSnapshot / IKernelBackend) as
+    compiled into _ref/libadaptq_ref_v2.so by build_ref.sh."""
+
+    PATH = os.path.join(_HERE, "_ref", "libadaptq_ref_v2.so")
+
+    @classmethod
+    def available(cls) -> bool:
+        return os.path.exists(cls.PATH)
+
+    def __init__(self):
+        L = self.lib = C.CDLL(self.PATH)
+        L.refv2_last_error.restype = C.c_char_p
+        L.refv2_create.restype = C.c_void_p
+        L.refv2_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]
+        L.refv2_destroy.argtypes = [C.c_void_p]
+        L.refv2_append.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]
+        L.refv2_compute.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]
+        L.refv2_token_pos.argtypes = [C.c_void_p]
+        L.refv2_snapshot_save.argtypes = [C.c_void_p, C.c_char_p]
+        L.refv2_snapshot_load.argtypes = [C.c_char_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int]
+        L.refv2_kernel_name.restype = C.c_char_p
+        L.refv2_kernel_fwht.argtypes = [_f32p, _i8p, C.c_int, C.c_int]
+        L.refv2_kernel_kdot_batch.argtypes = [_f32p, _u8p, C.c_size_t, _f32p, C.c_int, C.c_int, C.c_int, _f32p]
+        L.refv2_kernel_vaccum_batch.argtypes = [_f32p, _u8p, C.c_size_t, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
+
+    def error(self) -> str:
+        return self.lib.refv2_last_error().decode()
+
+    class Runtime:
+        def __init__(self, owner, n_layers, n_heads, dim, bits, capacity, v_mass=0.0):
+            self.o, self.dim = owner, dim
+            self.h = owner.lib.refv2_create(n_layers, n_heads, dim, bits, capacity, C.c_float(v_mass))
+            if not self.h:
+                raise RuntimeError(owner.error())
+
+        def append(self, layer, head, k, v):
+            k = np.ascontiguousarray(k, dtype=np.float32); v = np.ascontiguousarray(v, dtype=np.float32)
+            if self.o.lib.refv2_append(self.h, layer, head, _ptr(k, _f32p), _ptr(v, _f32p)) != 0:
+                raise RuntimeError(self.o.error())
+
+        def compute(self, layer, head, q):
+            q = np.ascontiguousarray(q, dtype=np.float32)
+            out = np.zeros(self.dim, dtype=np.float32)
+            n = self.o.lib.refv2_compute(self.h, layer, head, _ptr(q, _f32p), _ptr(out, _f32p))
+            if n < 0:
+                raise RuntimeError(self.o.error())
+            return out, n
+
+        def token_pos(self):
+            return self.o.lib.refv2_token_pos(self.h)
+
+        def save(self, path):
+            if self.o.lib.refv2_snapshot_save(self.h, str(path).encode()) != 0:
+                raise RuntimeError(self.o.error())
+
+        def close(self):
+            if self.h:
+                self.o.lib.refv2_destroy(self.h)
+                self.h = None
+
+        def __del__(self):
+            try:
+                self.close()
+            except Exception:
+                pass
+
+    def runtime(self, *a, **kw):
+        return RefV2.Runtime(self, *a, **kw)
+
+    def load_snapshot(self, path, max_heads=4096):
+        hdr = (C.c_int * 7)()
+        sizes = (C.c_int * max_heads)()
+        if self.lib.refv2_snapshot_load(str(path).encode(), hdr, sizes, max_heads) != 0:
+            raise RuntimeError(self.error())
+        keys = ("n_layers", "n_heads", "dim", "bits", "n_tokens", "n_head_blocks", "flags")
+        d = dict(zip(keys, list(hdr)))
+        d["cache_sizes"] = list(sizes)[:min(max_heads, d["n_head_blocks"])]
+        return d
+
+    def kernel_name(self):
+        return self.lib.refv2_kernel_name().decode()
+
+    def fwht(self, x, D, inverse=False):
+        y = np.ascontiguousarray(x, dtype=np.float32).copy()
+        D = np.ascontiguousarray(D, dtype=np.int8)
+        self.lib.refv2_kernel_fwht(_ptr(y, _f32p), _ptr(D, _i8p), len(y), 1 if inverse else 0)
+        return y
+
+    def kdot_batch(self, q_rot, rows, scales, padded, bits):
+        q = np.ascontiguousarray(q_rot, dtype=np.float32)
+        rows = np.ascontiguousarray(rows, dtype=np.uint8); sc = np.ascontiguousarray(scales, dtype=np.float32)
+        out = np.zeros(rows.shape[0], dtype=np.float32)
+        self.lib.refv2_kernel_kdot_batch(_ptr(q, _f32p), _ptr(rows, _u8p), rows.strides[0], _ptr(sc, _f32p), rows.shape[0],
+                                         padded, bits, _ptr(out, _f32p))
+        return out
+
+    def vaccum_batch(self, rows, scales, weights, padded, bits):
+        rows = np.ascontiguousarray(rows, dtype=np.uint8); sc = np.ascontiguousarray(scales, dtype=np.float32)
+        w = np.ascontiguousarray(weights, dtype=np.float32)
+        acc = np.zeros(padded, dtype=np.float32)
+        self.lib.refv2_kernel_vaccum_batch(_ptr(acc, _f32p), _ptr(rows, _u8p), rows.strides[0], _ptr(sc, _f32p), _ptr(w, _f32p),
+                                           rows.shape[0], padded, bits)
+        return acc
+
+
+def v2_head_seed(layer: int, head: int) -> int:
+    """Per-head seed of upstream's second stack (runtime/runtime_context.cpp:128)."""
+    return layer * 65537 + head

@@ -114,7 +114,7 @@ def unpack_rows(lib, rows, P, bits):
 SPARSE_MASS_SLACK = 1e-5
 
 
-def assert_sparse_close(got, head: "loader.Head", q, v_mass, what=""):
+def assert_sparse_close(got, head: "loader.Head", q, v_mass, what="", block=4):
     """Sparse-V output of the CUDA path against the oracle head `head` (which must be the
     C restatement).  Inside tolerance: fine.  Outside: accepted only if (a) the oracle's
     running mass at the neighbouring step boundary is within SPARSE_MASS_SLACK of v_mass
@@ -130,7 +130,7 @@ def assert_sparse_close(got, head: "loader.Head", q, v_mass, what=""):
             alts.append(int(count[-2]))                      # the GPU stopped one step earlier
         if len(mass) >= 1 and float(mass[-1]) - v_mass <= SPARSE_MASS_SLACK and int(count[-1]) < head.size:
             c = int(count[-1])
-            alts.append(c + 4 if c + 3 < head.size else c + 1)  # ... or one step later
+            alts.append(c + 4 if (block == 4 and c + 3 < head.size) else c + 1)  # ... or one step later
         for c in alts:
             try:
                 assert_close(got, head.compute_cut(q, c), what)

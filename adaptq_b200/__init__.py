@@ -5,11 +5,16 @@ NVIDIA B200 (sm_100a), behind upstream's own interfaces:
   implemented by ``libadaptq_b200.so``;
 * ``MHAContext`` (upstream's pybind class ``adaptq_py.MHAContext``);
 * ``Engine`` (upstream ``adaptq.Engine``), ``AdaptQAttention`` and its
-  many-sequence form ``BatchedAdaptQAttention``.
+  many-sequence form ``BatchedAdaptQAttention``; ``LayerStack`` (all layers of a
+  model behind one handle);
+* ``adaptq_b200.runtime`` (upstream's second stack: ``RuntimeContext``, AQSS v2
+  snapshots, ``IKernelBackend``) and ``adaptq_b200.hf_cache`` (Hugging Face
+  ``DynamicCache`` + fused attention function).
 """
 from ._lib import LIB_PATH, last_error, load  # noqa: F401
 from .core import Engine  # noqa: F401
 from .mha import MHAContext  # noqa: F401
+from .stack import LayerStack  # noqa: F401
 
 __version__ = "0.1.0"
 

@@ -59,6 +59,18 @@ SYMBOLS = {
     "adaptq_mha_info": (C.c_int, [C.c_void_p, C.POINTER(MhaInfo)]),
     "adaptq_mha_export_head": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_void_p, intp, intp, intp]),
+    "adaptq_stack_create": (C.c_void_p, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.c_uint64,
+                                         C.c_float, C.c_int]),
+    "adaptq_stack_destroy": (None, [C.c_void_p]),
+    "adaptq_stack_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "adaptq_stack_compute": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "adaptq_stack_decode_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
+    "adaptq_stack_reset": (C.c_int, [C.c_void_p]),
+    "adaptq_stack_kv_bytes": (C.c_size_t, [C.c_void_p]),
+    "adaptq_stack_parts": (C.c_int, [C.c_void_p]),
+    "adaptq_stack_layer_handle": (C.c_void_p, [C.c_void_p, C.c_int, intp]),
+    "adaptq_stack_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "adaptq_stack_synchronize": (C.c_int, [C.c_void_p]),
     # include/adaptq_runtime.h
     "adaptq_runtime_create": (C.c_void_p, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
     "adaptq_runtime_destroy": (None, [C.c_void_p]),

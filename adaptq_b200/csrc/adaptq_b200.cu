@@ -502,7 +502,7 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   const bool k_f32 = mirror || c.k_bits == 16;
   const bool v_f32 = mirror || c.v_bits == 16;
   const int items = a.heads_in_call * a.nq;
-  int want = std::max(1, (2 * g->sm_count + items - 1) / items);
+  int want = std::max(1, (2 * g->sm_count + items - 1) / items); // measured: more blocks per SM bring nothing
   int max_splits = std::max(1, (a.n + 63) / 64); // short spans: these shapes are latency-bound, so spread them wide
   a.n_splits = std::min(want, max_splits);
   a.span = (int)round_up((size_t)(a.n + a.n_splits - 1) / a.n_splits, 32);
@@ -624,7 +624,7 @@ bool launch_stream_t(Group *g, const StreamLaunch &a, int grid) {
 
 bool stream_supported(const CacheView &c) {
   if (c.padded == 128) return (c.k_bits == 4 || c.k_bits == 2) && (c.v_bits == 4 || c.v_bits == 2);
-  if (c.padded == 64) return c.k_bits == 4 && c.v_bits == 4;
+  if (c.padded == 64) return c.k_bits == 4 && (c.v_bits == 4 || c.v_bits == 2);
   return false;
 }
 
@@ -640,6 +640,7 @@ bool launch_stream_for_shape(Group *g, const StreamLaunch &a) {
     if (c.k_bits == 2 && c.v_bits == 2) return launch_stream_t<2, 8, 2, 8>(g, a, grid);
     return launch_stream_t<2, 8, 4, 16>(g, a, grid);
   }
+  if (c.v_bits == 2) return launch_stream_t<4, 8, 2, 4>(g, a, grid);
   return launch_stream_t<4, 8, 4, 8>(g, a, grid);
 }
 
@@ -1344,7 +1345,7 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
     return -1;
   }
   if (!stream_supported(c) || c.v_mass > 0.f || c.hyb > 0) {
-    set_error("adaptq_mha_compute_all_static: needs 2/4-bit K and V at head dim 64/128 (4-bit only at 64), dense V, no hybrid window");
+    set_error("adaptq_mha_compute_all_static: needs 2/4-bit K and V at head dim 64/128 (4-bit K only at 64), dense V, no hybrid window");
     return -1;
   }
   if (!g->uniform) {
@@ -1403,3 +1404,4 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
 } // extern "C"
 
 #include "runtime_v2_host.inc"
+#include "stack_host.inc"

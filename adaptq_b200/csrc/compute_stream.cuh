@@ -1,5 +1,5 @@
 // Streaming split-KV decode-attention kernel for the bandwidth-bound shapes
-// (2- or 4-bit K and V, padded dimension 64 or 128, dense V).
+// (2- or 4-bit K and V at padded dimension 128; 4-bit K with 2- or 4-bit V at 64; dense V).
 //
 // Replaces the same upstream code as compute_general.cuh -- the quantised
 // branch of AttentionHead::compute (attention/attention.cpp:526-563, :606-633)
@@ -198,13 +198,21 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   // (measured: fewer shuffles pay with the short rows, not with the long ones).
   constexpr int KLPT = KW == 16 ? 8 : 4;
   constexpr int KTPS = 32 / KLPT;                                           // tokens per warp step (K)
-  constexpr int KSTEPS = TKN / CS_WARPS / KTPS, VSTEPS = TVN / CS_WARPS / 4; // V: 4 tokens per warp step
-  constexpr int KWPL = KW / KLPT, VWPL = VW / 8;                            // words per lane
+  // V stream: 8 lanes per token (4 tokens per warp step); 4 lanes and 8 tokens with 16-byte rows
+  constexpr int VLPT = VW >= 8 ? 8 : 4;
+  constexpr int VTPS = 32 / VLPT;
+  constexpr int KSTEPS = TKN / CS_WARPS / KTPS, VSTEPS = TVN / CS_WARPS / VTPS;
+  constexpr int KWPL = KW / KLPT, VWPL = VW / VLPT;                         // words per lane
   constexpr int KC = KW * 4, VC = VW * 4;                                   // byte columns
   constexpr int KE = 8 / KB, VE = 8 / VB;                                   // coordinates per byte
   // 32 byte columns (2-bit V at dim 128, 4-bit at dim 64): bucket rows of 32 columns (128 bytes),
   // which leaves room for two more ring stages; the address is formed doubled and shifted back
-  constexpr bool COMPACT = VC == 32;
+  // 16 byte columns (2-bit V at dim 64): the same 128-byte rows hold TWO copies of the 16 columns
+  // side by side -- tokens 0..3 of a warp step add into the first, tokens 4..7 into the second --
+  // so the 32 lanes of a reduction still fall on 32 different banks; the fold adds the copies.
+  constexpr bool TWOCOPY = VC == 16;
+  constexpr bool COMPACT = VC == 32 || TWOCOPY;
+  constexpr int VCOLS = TWOCOPY ? 32 : VC;                                 // bucket columns, copies included
   constexpr int BUCKET_BYTES = COMPACT ? 32768 : CS_TABLE_BYTES;           // [256][32 or 64] 32-bit buckets
 
   extern __shared__ __align__(1024) unsigned char smem_stream[];
@@ -511,11 +519,13 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     else kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
   }
   const int krot = KLPT == 4 ? (KW == 16 ? (kg & 1) + 2 * (kg >> 2) : (kg & 3)) : tq;
+  // V stream lane roles: token vg of the warp step, word slot vwl of its row
+  const int vg = VLPT == 4 ? lane >> 2 : tq, vwl = VLPT == 4 ? lane & 3 : wl;
 #pragma unroll
-  for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+  for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? vwl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    const int kk = (k + tq) & 3;
+    const int kk = (k + vg) & 3;
     ksel[k] = 0x7604u | ((uint32_t)kk << 4); // result = {const.b0, data.byte[kk], const.b2, const.b3}
     const int kkk = (k + krot) & 3;
     kselk[k] = 0x7604u | ((uint32_t)kkk << 4);
@@ -524,9 +534,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
     // bucket rows are 64 columns (256 bytes), so the packed byte lands in address
     // bits 8..15 with one byte-permute
-    for (int m = 0; m < VWPL; ++m)
-      vconst[m][k] = COMPACT ? ((bucket_addr << 1) | (uint32_t)((4 * vword[m] + kk) << 3))
-                             : (bucket_addr | (uint32_t)((4 * vword[m] + kk) << 2));
+    for (int m = 0; m < VWPL; ++m) {
+      const int column = (TWOCOPY ? 16 * (vg >> 2) : 0) + 4 * vword[m] + kk;
+      vconst[m][k] = COMPACT ? ((bucket_addr << 1) | (uint32_t)(column << 3)) : (bucket_addr | (uint32_t)(column << 2));
+    }
   }
   float *table = reinterpret_cast<float *>(table_p);
   const float *kcb = c_cb[KB - 2];
@@ -705,12 +716,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     uint32_t *scu = reinterpret_cast<uint32_t *>(sc);
     const int len_pad = min(CS_SPAN_MAX, (len + TVN - 1) / TVN * TVN);
     // Stored in the order the V stream reads them: the VSTEPS weights that one lane
-    // needs from a tile (tokens 4s + tq of its warp's slice) sit side by side, so the
+    // needs from a tile (tokens VTPS*s + vg of its warp's slice) sit side by side, so the
     // lane fetches them with 128-bit loads.
     constexpr int TPWV = TVN / CS_WARPS;
     static_assert(CS_CONSUMERS % TPWV == 0, "a thread's tokens share their place in the warp slice");
     const int rem = tid % TPWV;
-    const int shift = (rem & 3) * VSTEPS + (rem >> 2) - rem; // the same for all of this thread's tokens
+    const int shift = (rem % VTPS) * VSTEPS + (rem / VTPS) - rem; // the same for all of this thread's tokens
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
       const int i = tid + r * CS_CONSUMERS;
@@ -722,7 +733,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       wait_full();
       const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
       uint32_t dv[VSTEPS][VWPL], wv[VSTEPS];
-      const uint4 *wp = reinterpret_cast<const uint4 *>(scu + (t - t0) + warp * TPWV + tq * VSTEPS);
+      const uint4 *wp = reinterpret_cast<const uint4 *>(scu + (t - t0) + warp * TPWV + vg * VSTEPS);
 #pragma unroll
       for (int s4 = 0; s4 < VSTEPS / 4; ++s4) {
         const uint4 w4 = wp[s4];
@@ -730,7 +741,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       }
 #pragma unroll
       for (int s = 0; s < VSTEPS; ++s) {
-        const int tok = warp * TPWV + 4 * s + tq;
+        const int tok = warp * TPWV + VTPS * s + vg;
 #pragma unroll
         for (int m = 0; m < VWPL; ++m) dv[s][m] = stw[tok * VW + vword[m]];
       }
@@ -755,10 +766,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // bucket once, clears it for the next item and feeds the VE coordinates packed
     // in that byte.
     {
-      constexpr int NPARTS = CS_CONSUMERS / VC, BPP = 256 / NPARTS;
+      constexpr int NPARTS = CS_CONSUMERS / VCOLS, BPP = 256 / NPARTS;
       constexpr int LOGB = BPP == 16 ? 4 : 5; // byte value = (part << LOGB) | i
       static_assert(BPP == 16 || BPP == 32, "16 or 32 byte values per thread");
-      const int col = tid % VC, part = tid / VC; // a warp shares `part`
+      const int col = tid % VCOLS, part = tid / VCOLS; // a warp shares `part`
       const float *vcb = c_cb[VB - 2];
       // The digit of coordinate e is bits [sh, sh+VB) of the byte value, sh = 8 - VB*(e+1).
       // With the loop over i unrolled it is a compile-time constant where those bits lie
@@ -801,13 +812,15 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         if (sh >= LOGB) av[e] = psum[e] * cmix[e][0];
       }
       // sc[] is free (the V stream has finished with the weights): use it as fold space
+      constexpr int NG = TWOCOPY ? 2 * NPARTS : NPARTS; // partial accumulators per coordinate
+      const int grp = TWOCOPY ? 2 * part + (col >> 4) : part, ccol = TWOCOPY ? (col & 15) : col;
 #pragma unroll
-      for (int e = 0; e < VE; ++e) sc[part * P + col * VE + e] = av[e] * inv_fx;
+      for (int e = 0; e < VE; ++e) sc[grp * P + ccol * VE + e] = av[e] * inv_fx;
       consumer_sync();
       if (tid < P) { // hand the finished item to the helper warp and move on
         float t = 0.f;
 #pragma unroll
-        for (int g = 0; g < NPARTS; ++g) t += sc[g * P + tid];
+        for (int g = 0; g < NG; ++g) t += sc[g * P + tid];
         const int ab = idx & 1;
         guarded_wait(&aempty[ab], (((uint32_t)idx >> 1) & 1u) ^ 1u);
         float *dst = accb + ab * ACC_PITCH;

@@ -118,7 +118,7 @@ int adaptq_mha_merge_from_peers(adaptq_mha_t mha, const float *gather_buf,
  *
  *  - queries, outs: DEVICE memory, float [n_heads][queries_per_head][dim].
  *  - Shapes of the streaming kernel only: K and V at 2 or 4 bits with head
- *    dim 128 (4/4 bits at dim 64), v_mass <= 0, hybrid_thresh == 0, all heads
+ *    dim 128 (4-bit K with 2- or 4-bit V at dim 64), v_mass <= 0, hybrid_thresh == 0, all heads
  *    holding the same number of tokens.  Anything else returns -1.
  *  - The split-KV partials live in a 4 MiB array inside the library image
  *    (held on every GPU that loads the library, until the process exits)
@@ -136,6 +136,42 @@ int adaptq_mha_merge_from_peers(adaptq_mha_t mha, const float *gather_buf,
  * Returns the token count, or -1 with adaptq_last_error() set. */
 int adaptq_mha_compute_all_static(adaptq_mha_t mha, const float *queries,
                                   int queries_per_head, float *outs);
+
+/* Layer stacks.  Upstream keeps one Engine per transformer layer (seed
+ * 42 ^ layer, its README and benchmarks) and walks layers and heads in Python,
+ * one C call per head (adaptq/core.py:53-57, :70-72): 2 x layers x heads calls
+ * per token.  A stack holds the caches of ALL layers -- layer l is what
+ * Engine(dim, n_heads, k_bits[l], v_bits[l], capacity, seed ^ l, v_mass,
+ * hybrid_thresh) holds -- and moves a token through every layer in one call.
+ * Consecutive layers with the same (k_bits, v_bits) share one multi-head handle
+ * (a "part"); the parts run on CUDA streams of their own, so e.g. the FP32-key
+ * first layer of a layer-aware policy overlaps the quantized layers behind it.
+ * Buffers are float [n_layers][n_heads][dim] (append: [n_tokens][n_layers]
+ * [n_heads][dim]), host or device; with device buffers nothing synchronises.
+ * Additions without a counterpart upstream; results equal the per-layer loop. */
+typedef void *adaptq_stack_t;
+adaptq_stack_t adaptq_stack_create(int n_layers, int n_heads, int dim,
+                                   const int *k_bits, const int *v_bits,
+                                   int capacity, uint64_t seed, float v_mass,
+                                   int hybrid_thresh);
+void adaptq_stack_destroy(adaptq_stack_t st);
+int adaptq_stack_append(adaptq_stack_t st, const float *keys, const float *vals,
+                        int n_tokens, int token_pos0);
+int adaptq_stack_compute(adaptq_stack_t st, const float *queries, float *outs);
+/* append(keys, vals, 1) + compute(queries) for every layer: 2 launches per part */
+int adaptq_stack_decode_step(adaptq_stack_t st, const float *keys,
+                             const float *vals, const float *queries,
+                             float *outs, int token_pos);
+int adaptq_stack_reset(adaptq_stack_t st);
+size_t adaptq_stack_kv_bytes(adaptq_stack_t st);
+/* number of parts; the multi-head handle that holds `layer` and the index of the
+ * layer's first head inside it (for adaptq_mha_export_head, adaptq_mha_info) */
+int adaptq_stack_parts(adaptq_stack_t st);
+adaptq_mha_t adaptq_stack_layer_handle(adaptq_stack_t st, int layer, int *first_head);
+int adaptq_stack_set_stream(adaptq_stack_t st, void *cuda_stream);
+/* wait for the stack's work and report a kernel that gave up waiting (see
+ * adaptq_mha_synchronize) */
+int adaptq_stack_synchronize(adaptq_stack_t st);
 
 /* Use `cuda_stream` (a cudaStream_t; NULL = the default stream) for all
  * further work of this handle. */

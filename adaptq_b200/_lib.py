@@ -90,6 +90,7 @@ SYMBOLS = {
     "adaptq_kernel_kdot_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "adaptq_kernel_vaccum_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "adaptq_kernel_backend_name": (C.c_char_p, []),
+    "adaptq_inject_failure": (C.c_int, [C.c_int, C.c_int]),
     "adaptq_kernel_launches": (C.c_ulonglong, []),
     "adaptq_set_kernel_policy": (C.c_int, [C.c_int]),
 }

@@ -47,6 +47,42 @@ extern "C" int adaptq_set_kernel_policy(int policy) {
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// Failure seam for tests: the three host-side calls whose failure the library must
+// survive -- device allocation, page-locked host allocation, kernel launch -- go
+// through these wrappers.  adaptq_inject_failure(kind, nth) makes the nth upcoming
+// call of that kind report failure WITHOUT touching the device (nothing faults,
+// nothing is launched), so the error paths can be exercised on a healthy GPU.
+// ---------------------------------------------------------------------------
+enum { FAIL_DEVICE_ALLOC = 1, FAIL_PINNED_ALLOC = 2, FAIL_LAUNCH = 3 };
+static std::atomic<int> g_fail_in[4] = {};
+static bool injected(int kind) {
+  int v = g_fail_in[kind].load();
+  while (v > 0) {
+    if (g_fail_in[kind].compare_exchange_weak(v, v - 1)) return v == 1;
+  }
+  return false;
+}
+extern "C" int adaptq_inject_failure(int kind, int nth) {
+  if (kind < FAIL_DEVICE_ALLOC || kind > FAIL_LAUNCH || nth < 0) { set_error("adaptq_inject_failure: kind must be 1..3 and nth >= 0"); return -1; }
+  g_fail_in[kind].store(nth);
+  return 0;
+}
+static cudaError_t device_malloc(void **p, size_t bytes) {
+  if (injected(FAIL_DEVICE_ALLOC)) { *p = nullptr; return cudaErrorMemoryAllocation; }
+  return cudaMalloc(p, bytes);
+}
+static cudaError_t pinned_malloc(void **p, size_t bytes) {
+  if (injected(FAIL_PINNED_ALLOC)) { *p = nullptr; return cudaErrorMemoryAllocation; }
+  return cudaMallocHost(p, bytes);
+}
+// The status of the launch just made (cudaGetLastError), or an injected failure.
+static cudaError_t launch_status() {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && injected(FAIL_LAUNCH)) return cudaErrorLaunchFailure;
+  return e;
+}
+
 #define CUDA_TRY(expr, what)                                                            \
   do {                                                                                  \
     cudaError_t e__ = (expr);                                                           \
@@ -86,6 +122,9 @@ struct Group {
   int *d_status = nullptr;
   size_t device_bytes = 0;
   std::mutex mu;
+#ifdef ADAPTQ_CHECKED
+  std::vector<std::pair<const unsigned char *, const char *>> canaries; // (first byte behind a buffer, its name)
+#endif
   // decode-step pipeline (host buffers): copy streams and per-chunk events, made on first use
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   std::vector<cudaEvent_t> ev;
@@ -148,18 +187,48 @@ void free_group(Group *g) {
   delete g;
 }
 
+// Checked build: every buffer of a handle is followed by AQ_CANARY_BYTES of a fixed pattern
+// that adaptq_mha_synchronize verifies; a kernel that writes past a buffer is caught there.
+#ifdef ADAPTQ_CHECKED
+constexpr size_t AQ_CANARY_BYTES = 256;
+constexpr int AQ_CANARY_BYTE = 0xA5;
+#endif
+
 bool alloc(void **p, size_t bytes, Group *g, const char *what) {
   *p = nullptr;
   if (bytes == 0) bytes = 16;
-  cudaError_t e = cudaMalloc(p, bytes);
+#ifdef ADAPTQ_CHECKED
+  const size_t tail = AQ_CANARY_BYTES;
+#else
+  const size_t tail = 0;
+#endif
+  cudaError_t e = device_malloc(p, bytes + tail);
   if (e != cudaSuccess) {
     cudaGetLastError();
     set_error("%s: device allocation of %zu bytes failed: %s", what, bytes, cudaGetErrorString(e));
     return false;
   }
+#ifdef ADAPTQ_CHECKED
+  cudaMemset(static_cast<unsigned char *>(*p) + bytes, AQ_CANARY_BYTE, tail);
+  g->canaries.emplace_back(static_cast<unsigned char *>(*p) + bytes, what);
+#endif
   g->device_bytes += bytes;
   return true;
 }
+
+#ifdef ADAPTQ_CHECKED
+void forget_canary(Group *g, const void *base) { // the buffer is about to be freed
+  // buffers are separate allocations, so the closest guard above `base` is the one behind it
+  size_t best = g->canaries.size();
+  for (size_t i = 0; i < g->canaries.size(); ++i)
+    if (g->canaries[i].first > static_cast<const unsigned char *>(base) &&
+        (best == g->canaries.size() || g->canaries[i].first < g->canaries[best].first))
+      best = i;
+  if (best != g->canaries.size()) g->canaries.erase(g->canaries.begin() + best);
+}
+#else
+inline void forget_canary(Group *, const void *) {}
+#endif
 
 // Rademacher signs as upstream core/fwht.cpp:21-27, stored one bit per sign.
 void sign_words_for(uint64_t seed, int padded, uint32_t *words, int n_words) {
@@ -254,7 +323,7 @@ PtrKind ptr_kind(const void *p) {
 bool ensure_stage(Group *g, size_t dev_bytes, size_t host_bytes) {
   if (dev_bytes > g->stage_bytes) {
     CUDA_TRY(cudaStreamSynchronize(g->stream), "staging");
-    if (g->d_stage) { cudaFree(g->d_stage); g->device_bytes -= g->stage_bytes; }
+    if (g->d_stage) { forget_canary(g, g->d_stage); cudaFree(g->d_stage); g->device_bytes -= g->stage_bytes; }
     g->d_stage = nullptr; g->stage_bytes = 0;
     size_t nb = round_up(dev_bytes, 256);
     if (!alloc(&g->d_stage, nb, g, "staging")) return false;
@@ -265,7 +334,7 @@ bool ensure_stage(Group *g, size_t dev_bytes, size_t host_bytes) {
     if (g->h_stage) cudaFreeHost(g->h_stage);
     g->h_stage = nullptr; g->h_stage_bytes = 0;
     size_t nb = round_up(host_bytes, 4096);
-    CUDA_TRY(cudaMallocHost(&g->h_stage, nb), "staging (pinned host)");
+    CUDA_TRY(pinned_malloc(&g->h_stage, nb), "staging (pinned host)");
     g->h_stage_bytes = nb;
   }
   return true;
@@ -278,7 +347,7 @@ constexpr int MAX_COUNTED_ITEMS = (int)(SCRATCH_HEADER / sizeof(int));
 bool ensure_scratch(Group *g, size_t bytes) {
   if (bytes <= g->scratch_bytes) return true;
   CUDA_TRY(cudaStreamSynchronize(g->stream), "scratch");
-  if (g->d_scratch_base) { cudaFree(g->d_scratch_base); g->device_bytes -= g->scratch_bytes + SCRATCH_HEADER; }
+  if (g->d_scratch_base) { forget_canary(g, g->d_scratch_base); cudaFree(g->d_scratch_base); g->device_bytes -= g->scratch_bytes + SCRATCH_HEADER; }
   g->d_scratch_base = nullptr; g->d_scratch = nullptr; g->d_counters = nullptr; g->scratch_bytes = 0;
   size_t nb = round_up(bytes + bytes / 4, 256);
   if (!alloc(&g->d_scratch_base, nb + SCRATCH_HEADER, g, "scratch")) return false;
@@ -314,10 +383,22 @@ bool check_status(Group *g, const char *fn) {
   CUDA_TRY(cudaMemcpyAsync(st, g->d_status, sizeof(int), cudaMemcpyDeviceToHost, g->stream), fn);
   CUDA_TRY(cudaStreamSynchronize(g->stream), fn);
   if (st[0] != 0) {
-    set_error("%s: a kernel gave up waiting for a memory transfer (status %d)", fn, st[0]);
+    if (st[0] >= 10) set_error("%s: a device-side index check failed (status %d); the access was skipped", fn, st[0]);
+    else set_error("%s: a kernel gave up waiting for a memory transfer (status %d)", fn, st[0]);
     cudaMemsetAsync(g->d_status, 0, sizeof(int), g->stream);
     return false;
   }
+#ifdef ADAPTQ_CHECKED
+  unsigned char tail[AQ_CANARY_BYTES];
+  for (auto &cn : g->canaries) {
+    CUDA_TRY(cudaMemcpy(tail, cn.first, AQ_CANARY_BYTES, cudaMemcpyDeviceToHost), fn);
+    for (size_t i = 0; i < AQ_CANARY_BYTES; ++i)
+      if (tail[i] != AQ_CANARY_BYTE) {
+        set_error("%s: the guard bytes behind a device buffer (%s) were overwritten at offset %zu", fn, cn.second, i);
+        return false;
+      }
+  }
+#endif
   return true;
 }
 
@@ -351,7 +432,7 @@ bool launch_rows(Group *g, const AppendLaunch &a) {
   int grid = (int)std::min<long long>(tiles, (long long)g->sm_count * AT_BLOCKS_PER_SM);
   kern<<<grid, AT_THREADS, SMEM, g->stream>>>(a);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "append");
+  CUDA_TRY(launch_status(), "append");
   return true;
 }
 
@@ -377,7 +458,7 @@ bool launch_pair(Group *g, const AppendLaunch &ak, const AppendLaunch &av) {
   int gx = (int)std::min<long long>(tiles, (long long)g->sm_count * (AT_BLOCKS_PER_SM / 2));
   kern<<<dim3(gx, 2), AT_THREADS, SMEM, g->stream>>>(ak, av.src);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "append");
+  CUDA_TRY(launch_status(), "append");
   return true;
 }
 template <int P, int KB>
@@ -415,7 +496,7 @@ bool launch_append_one(Group *g, AppendLaunch a, int src_row_align_ok) {
   size_t smem = (size_t)GEN_WARPS * c.padded * sizeof(float);
   append_general_kernel<<<grid, GEN_WARPS * 32, smem, g->stream>>>(a);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "append");
+  CUDA_TRY(launch_status(), "append");
   return true;
 }
 
@@ -527,13 +608,13 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   dim3 grid(a.n_splits, a.heads_in_call, a.nq);
   compute_general_kernel<<<grid, CG_THREADS, smem, g->stream>>>(a);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "compute");
+  CUDA_TRY(launch_status(), "compute");
   if (!direct && !fused) {
     merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
         a.partial, (size_t)items * partial_floats(c), a.n_splits, c, a.head0, a.nq,
         want_partial_out ? partial_out : a.out, v_f32 ? 1 : 0, want_partial_out ? 1 : 0, mirror ? a.n : 0);
     ++g_launches;
-    CUDA_TRY(cudaGetLastError(), "compute (merge)");
+    CUDA_TRY(launch_status(), "compute (merge)");
   }
   return true;
 }
@@ -551,7 +632,7 @@ bool launch_logits(Group *g, ComputeLaunch &a, float *w, int ws) {
   if (!ensure_general_smem(g, smem)) return false;
   compute_general_kernel<<<dim3(a.n_splits, a.heads_in_call, a.nq), CG_THREADS, smem, g->stream>>>(a);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "compute (logits)");
+  CUDA_TRY(launch_status(), "compute (logits)");
   return true;
 }
 
@@ -561,9 +642,9 @@ bool launch_sparse_fused_t(Group *g, const ComputeLaunch &a, const float *w, int
   static int configured[MAX_DEVICES] = {};
   auto kern = sparse_fused_kernel<ITEMS>;
   if (!ensure_smem_limit(kern, configured, g->device, smem, "compute (sparse V)")) return false;
-  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, a.rot, g->c, a.head0, a.nq, a.out);
+  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, a.rot, g->c, a.head0, a.nq, a.out, g->d_status);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "compute (sparse V)");
+  CUDA_TRY(launch_status(), "compute (sparse V)");
   return true;
 }
 
@@ -605,7 +686,7 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
   CUDA_TRY(e, "compute (sparse-V sort)");
   sparse_accumulate_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(sw, so, ws, a.n, c, a.head0, a.nq, a.out);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "compute (sparse V)");
+  CUDA_TRY(launch_status(), "compute (sparse V)");
   return true;
 }
 
@@ -618,7 +699,7 @@ bool launch_stream_t(Group *g, const StreamLaunch &a, int grid) {
   if (!ensure_smem_limit(kern, configured, g->device, CS_SMEM_BYTES, "compute")) return false;
   kern<<<grid, CS_THREADS, CS_SMEM_BYTES, g->stream>>>(a);
   ++g_launches;
-  CUDA_TRY(cudaGetLastError(), "compute");
+  CUDA_TRY(launch_status(), "compute");
   return true;
 }
 
@@ -709,7 +790,7 @@ bool launch_stream(Group *g, const ComputeLaunch &ca, bool want_partial_out, flo
         a.partial, (size_t)items_base * partial_floats(c), a.n_splits, c, a.head0, a.nq,
         want_partial_out ? partial_out : a.out, 0, want_partial_out ? 1 : 0, 0);
     ++g_launches;
-    CUDA_TRY(cudaGetLastError(), "compute (merge)");
+    CUDA_TRY(launch_status(), "compute (merge)");
   }
   return true;
 }
@@ -736,6 +817,7 @@ bool compute_device(Group *g, const float *dq, float *dout, int head0, int heads
   ComputeLaunch a{};
   a.c = c; a.q = dq; a.out = dout; a.head0 = head0; a.heads_in_call = heads_in_call; a.nq = nq; a.n = st.size;
   a.rot = (int)(((long long)st.head - st.size + c.cap) % c.cap); // st.size > 0, so c.cap > 0
+  a.status = g->d_status;
   a.use_mirror = (c.hyb > 0 && st.size <= c.hyb && st.mirror == st.size) ? 1 : 0;
   const bool quant = c.k_bits != 16 && c.v_bits != 16;
   if (partial_out) return launch_general_or_stream(g, a, true, dout);
@@ -947,7 +1029,11 @@ size_t adaptq_mha_total_kv_bytes(adaptq_mha_t h) {
 }
 
 unsigned int adaptq_features(void) { return ADAPTQ_FEAT_HYBRID | ADAPTQ_FEAT_SPARSE_V | ADAPTQ_FEAT_CUDA_SM100; }
+#ifdef ADAPTQ_CHECKED
+const char *adaptq_version(void) { return "3.2.0-sm100a-checked"; }
+#else
 const char *adaptq_version(void) { return "3.2.0-sm100a"; }
+#endif
 
 // ---- batched additions ---------------------------------------------------------------
 
@@ -1178,7 +1264,7 @@ int adaptq_mha_compute_partial_to_peers(adaptq_mha_t h, const float *queries, in
   if (g->u.size == 0) {
     deliver_empty_kernel<<<(items + 127) / 128, 128, 0, g->stream>>>(ps, items, (int)partial_floats(c));
     ++g_launches;
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_status();
     if (e != cudaSuccess) { set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e)); return -1; }
     return 0;
   }
@@ -1204,7 +1290,7 @@ int adaptq_mha_merge_from_peers(adaptq_mha_t h, const float *gather_buf, const u
   merge_peers_kernel<<<(items + 3) / 4, 128, 4 * c.padded * sizeof(float), g->stream>>>(
       gather_buf, (size_t)items * partial_floats(c), world, flags, expected, g->d_status, c, 0, queries_per_head, items, outs);
   ++g_launches;
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_status();
   if (e != cudaSuccess) { set_error("%s: CUDA error: %s", fn, cudaGetErrorString(e)); return -1; }
   return 0;
 }
@@ -1234,7 +1320,7 @@ int adaptq_mha_merge_partials(adaptq_mha_t h, const float *partials, int n_parts
   merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
       dp, (size_t)items * partial_floats(c), n_parts, c, 0, queries_per_head, dout, 0, 0, 0);
   ++g_launches;
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_status();
   if (e == cudaSuccess && okd != PK_DEVICE) {
     void *hdst = okd == PK_HOST_PINNED ? (void *)outs : (void *)(static_cast<char *>(g->h_stage) + off_out);
     e = cudaMemcpyAsync(hdst, dout, ob, cudaMemcpyDeviceToHost, g->stream);
@@ -1393,7 +1479,7 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
     merge_partials_kernel<<<items_base, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
         scratch, (size_t)items_base * partial_floats(c), a.n_splits, c, 0, queries_per_head, outs, 0, 0, 0);
     ++g_launches;
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_status();
     if (e != cudaSuccess) { set_error("adaptq_mha_compute_all_static: CUDA error: %s", cudaGetErrorString(e)); return -1; }
   }
   return n;

@@ -175,6 +175,7 @@ __device__ __forceinline__ void append_item_general(const AppendLaunch &a, long 
     for (int i = lane; i < dim; i += 32) m[i] = buf[i];
   }
   if (!p.store) { __syncwarp(); return; }
+  if (!AQ_CHECK(a.status, p.slot >= 0 && p.slot < c.cap && p.h >= 0 && p.h < c.n_heads, 11)) { __syncwarp(); return; }
   uint8_t *row = (a.which ? c.v_slab : c.k_slab) + (size_t)p.h * (a.which ? c.v_stride : c.k_stride) + (size_t)p.slot * rowb;
   float *scale = (a.which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride + p.slot;
   if (bits == 16) {
@@ -532,6 +533,8 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const fl
     const float norm = nrm.x;
     const bool skip = BITS != 16 && norm < 0.f;
     if (skip) p.store = p.mirror = false;
+    if ((p.store || p.mirror) && !AQ_CHECK(a.status, p.slot >= 0 && p.slot < c.cap && p.h >= 0 && p.h < c.n_heads, 11))
+      p.store = p.mirror = false;
     unsigned long long xp[EPL / 2]; // coordinates (2i, 2i+1) of this quarter, packed
     {
       const bool have = p.store || p.mirror;

@@ -6,6 +6,21 @@
 namespace aq {
 
 // ---------------------------------------------------------------------------
+// Checked build (-DADAPTQ_CHECKED): device-side index checks that never trap.  A
+// failed check records its code in the launch's status word (the host reports it
+// through adaptq_mha_synchronize) and the guarded access is skipped, so the context
+// stays usable.  In the normal build the macro is the constant `true`.
+//   11 append: slot or head outside the cache      12 compute: token row outside the cache
+//   13 streaming kernel: a stage copy would read past the head's slab
+//   14 partial / output slot outside its buffer    15 sparse V: token index outside the cache
+// ---------------------------------------------------------------------------
+#ifdef ADAPTQ_CHECKED
+#define AQ_CHECK(status_ptr, cond, code) ((cond) ? true : (atomicExch((status_ptr), (code)), false))
+#else
+#define AQ_CHECK(status_ptr, cond, code) (true)
+#endif
+
+// ---------------------------------------------------------------------------
 // Lloyd-Max N(0,1) centroids and their midpoint decision thresholds.
 // Same numbers as upstream core/codebook.cpp:32-62 (centroids) and :67-100
 // (thresholds).  The thresholds are written as the expression (a+b)*0.5f so

@@ -33,6 +33,7 @@ struct ComputeLaunch {
   int n_splits, span; // tokens per split
   int chunk;          // tokens per shared-memory pass
   int mode;
+  int *status;  // checked build: where a failed index check is recorded
   // mode 1 with fused merge: the block that completes an item's last partial merges them
   int *counters;      // [heads_in_call*nq] arrival counts, zero before and after every launch (nullptr: no fused merge)
   float *final_out;   // outputs (or combined partials when final_to_partial)
@@ -219,7 +220,8 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   const float *vsc = c.v_scale + (size_t)h * c.s_stride;
   const float *mir = mirror ? c.mirror + (size_t)h * c.mirror_stride : nullptr;
 
-  const int t_begin = min(a.n, split * a.span), t_end = min(a.n, t_begin + a.span);
+  int t_begin = min(a.n, split * a.span), t_end = min(a.n, t_begin + a.span);
+  if (!AQ_CHECK(a.status, t_end <= c.cap && h >= 0 && h < c.n_heads, 12)) t_begin = t_end = 0; // nothing is read
 
   // Each thread owns output columns j = jcol + r*CG_THREADS of token group tg.
   const int TG = P < CG_THREADS ? CG_THREADS / P : 1;
@@ -326,6 +328,7 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
     const int item = hl * a.nq + qi;
     const size_t part_stride = (size_t)a.heads_in_call * a.nq * (size_t)(2 + P);
     float *pp = a.partial + (size_t)split * part_stride + (size_t)item * (size_t)(2 + P);
+    if (!AQ_CHECK(a.status, split < a.n_splits && item < a.heads_in_call * a.nq, 14)) return;
     if (tid == 0) { pp[0] = run_m; pp[1] = run_l; }
     for (int j = tid; j < P; j += CG_THREADS) pp[2 + j] = vec[j];
     if (a.counters == nullptr) return;

@@ -46,7 +46,7 @@ __device__ __forceinline__ float sp_block_reduce(float v, float *red, bool is_ma
 
 template <int ITEMS>
 __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *logits, int w_stride, int n, int rot, CacheView c,
-                                                                  int head0, int nq, float *out) {
+                                                                  int head0, int nq, float *out, int *status) {
   using S = SparseSmem<ITEMS>;
   using Sort = typename S::Sort;
   extern __shared__ __align__(16) unsigned char smem_sp[];
@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   const float *vsc = c.v_scale + (size_t)h * c.s_stride;
   const float *vcb = c_cb[c.v_bits - 2];
   const float isp = 1.f / sqrtf((float)P);
-  for (int i = tid; i < count; i += SP_THREADS) s_w[i] = s_w[i] * vsc[s_tok[i]] * isp;
+  for (int i = tid; i < count; i += SP_THREADS)
+    if (AQ_CHECK(status, s_tok[i] >= 0 && s_tok[i] < c.cap, 15)) s_w[i] = s_w[i] * vsc[s_tok[i]] * isp;
   __syncthreads();
   // ---- V rows of the chosen tokens: thread = (column, token group) ----------------------------
   const int TG = P < SP_THREADS ? SP_THREADS / P : 1;
@@ -135,8 +136,10 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
     if (j >= P || (P < SP_THREADS && r > 0)) break;
     float av = 0.f;
 #pragma unroll 4
-    for (int i = tg; i < count; i += TG)
+    for (int i = tg; i < count; i += TG) {
+      if (!AQ_CHECK(status, s_tok[i] >= 0 && s_tok[i] < c.cap, 15)) continue;
       av += s_w[i] * vcb[unpack_at(vbase + (size_t)s_tok[i] * c.v_row, j, c.v_bits)];
+    }
     acc[r] = av;
   }
   __syncthreads(); // bsum is dead; reuse the scratch for the fold

@@ -337,6 +337,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
           const uint32_t bytes = ((uint32_t)(cnt * rowb) + 15u) & ~15u;
           // scales: rounded up to 16 bytes; the per-head scale rows carry 128 bytes of padding
           const uint32_t sbytes = pass ? 0u : (((uint32_t)cnt * 4u + 15u) & ~15u);
+          // a copy may run into the 128-byte slack behind a head's rows, never past it
+          if (!AQ_CHECK(a.status, (size_t)t * rowb + bytes <= (pass == 0 ? c.k_stride : pass == 1 ? (size_t)c.s_stride * 4 : c.v_stride) &&
+                                      h >= 0 && h < c.n_heads, 13)) {
+            *reinterpret_cast<volatile int *>(s_fail) = 1; // consumers stop waiting; the block drains
+            return;
+          }
           mbar_expect_tx(&full[stage], bytes + sbytes);
           bulk_g2s(stage_ptr(stage), src + (size_t)t * rowb, bytes, &full[stage]);
           if (sbytes) bulk_g2s(ks_area + (size_t)stage * KS_STAGE_BYTES, ksb + t, sbytes, &full[stage]);
@@ -419,6 +425,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
         deliver_to_peers(hq, mx, ls, v);
       } else if (a.n_splits > 1 || a.force_partial) {
         float *pp = a.partial + ((size_t)split * items_base + hq) * (size_t)(2 + P);
+        if (!AQ_CHECK(a.status, split < a.n_splits && hq < items_base, 14)) continue;
         if (lane == 0) { pp[0] = mx; pp[1] = ls; }
 #pragma unroll
         for (int e = 0; e < EPL; ++e) pp[2 + EPL * lane + e] = v[e];

@@ -173,6 +173,16 @@ int adaptq_stack_set_stream(adaptq_stack_t st, void *cuda_stream);
  * adaptq_mha_synchronize) */
 int adaptq_stack_synchronize(adaptq_stack_t st);
 
+/* Test hook: make the nth upcoming host-side call of one kind report failure
+ * without touching the device -- kind 1: device allocation, 2: page-locked host
+ * allocation, 3: kernel launch (the check after a launch sees an error; the
+ * kernel itself still runs).  nth = 0 switches the kind off.  Lets tests walk
+ * every error path of this library (NULL / -1 returns, error text, no leaked
+ * memory, handle still usable) on a healthy GPU; nothing faults.  Upstream has
+ * no counterpart (its allocation failures throw through the C ABI,
+ * cache/ring_buffer.cpp:71-76). */
+int adaptq_inject_failure(int kind, int nth);
+
 /* Use `cuda_stream` (a cudaStream_t; NULL = the default stream) for all
  * further work of this handle. */
 int adaptq_mha_set_stream(adaptq_mha_t mha, void *cuda_stream);

@@ -731,6 +731,7 @@ bool launch_stream_for_shape(Group *g, const StreamLaunch &a) {
 // and the item count should fill whole waves of persistent blocks.
 void plan_spans(int n, int items_base, int sms, int &n_splits, int &span) {
   const int G = 64;
+
   const int n_pad = (int)round_up((size_t)n, G);
   const int min_splits = (n + CS_SPAN_MAX - 1) / CS_SPAN_MAX;
   double best = -1.0;

@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
                 L += __ldcg(q2 + 1) * w;
               }
               const int cnt = min(32, a.n_splits - p0);
-#pragma unroll 4
+#pragma unroll 8
               for (int j = 0; j < cnt; ++j) {
                 const float wj = __shfl_sync(0xffffffffu, w, j);
                 const float2 *row = reinterpret_cast<const float2 *>(base + (size_t)(p0 + j) * pstride + 2 + EPL * lane);

@@ -512,15 +512,21 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
         def step_single():
             ctx.compute_all(q, out=o[:, 0])
 
-        def timed(fn):
+        def timed(fn, queued=True):
+            """Median device time of one step (CUDA events around it), max over ranks.  L2 is flushed
+            before every step.  queued=True: the step is enqueued while the flush kernel still runs, so
+            the events bracket the step's own device work; queued=False: the device is idle when the
+            step is issued, so the figure also contains the host's launch latency."""
             for _ in range(max(3, warmup)):
                 fn()
             samples = []
             for _ in range(steps):
-                flush.fill_(1)
                 torch.cuda.synchronize()
                 if dist is not None:
                     dist.barrier()
+                    torch.cuda.synchronize()
+                flush.fill_(1)
+                if not queued:
                     torch.cuda.synchronize()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
@@ -541,6 +547,7 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
                "effective_kv_gbs_all_ranks": alg / us_total / 1e3, "local_kernel_gbs_per_gpu": alg / world / us_local / 1e3,
                "local_kernel_frac_of_peak": alg / world / us_local / 1e3 / peak,
                "algorithmic_bytes": alg, "tokens_per_rank": local_n}
+        res["us_per_step_incl_host_launch"] = timed(step_sharded, queued=False)
         res["exchange_share"] = max(0.0, us_total - us_local) / us_total
         res["frac_of_peak_all_ranks"] = alg / us_total / 1e3 / (peak * world)
         if world == 1:
@@ -713,7 +720,9 @@ def run_ours(args):
             if rank == 0:
                 line["longctx"] = {"workload": "one sequence, 32 KV heads, dim 128, context 131072, Student-t(3), KV range "
                                                "split by token over the ranks (BASELINE configs[4]); L2 flushed before "
-                                               "every timed step; medians; max over ranks", "scaling": "strong",
+                                               "every timed step, the step enqueued behind the flush (device time of the "
+                                               "step; us_per_step_incl_host_launch: issued on an idle device); medians; "
+                                               "max over ranks", "scaling": "strong",
                                    "n_gpus": world, "results": lres}
         except Exception as ex:
             line["longctx"] = {"error": repr(ex)}

@@ -129,13 +129,20 @@ template <int BITS> __device__ __forceinline__ void build_quant_table(uint2 *qta
   }
 }
 
-template <int BITS> __device__ __forceinline__ uint32_t quantize_lookup(float v, uint32_t qtab_addr) {
-  // floor(4v) + 64 lands in the low mantissa bits of 2^23 + 64 + 4v rounded down
+// The search for one coordinate, with the index added into `word` at bit position SHIFT:
+// floor(4v) + 64 lands in the low mantissa bits of 2^23 + 64 + 4v rounded down, the count of
+// thresholds below that bucket goes into the word with one multiply-add, and the last
+// `v >= t` decision (upstream's comparison, core/codebook.cpp:128-131) with one predicated add.
+template <int BITS, uint32_t SHIFT> __device__ __forceinline__ void quantize_into_word(uint32_t &word, float v, uint32_t qtab_addr) {
   const float t = __fmaf_rd(v, 4.0f, 8388608.0f + 64.0f);
-  const uint32_t addr = (__float_as_uint(t) << 3) + (qtab_addr - 0x58000000u); // (bits - 0x4B000000) * 8
-  uint2 e;
-  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "r"(addr));
-  return e.y + (v >= __uint_as_float(e.x) ? 1u : 0u);
+  const uint32_t addr = (__float_as_uint(t) << 3) + (qtab_addr - 0x58000000u);
+  asm("{\n\t.reg .b32 thr, cnt;\n\t.reg .pred p;\n\t"
+      "ld.shared.v2.b32 {thr, cnt}, [%1];\n\t"
+      "mad.lo.u32 %0, cnt, %3, %0;\n\t"
+      "setp.ge.f32 p, %2, thr;\n\t"
+      "@p add.u32 %0, %0, %3;\n\t}"
+      : "+r"(word)
+      : "r"(addr), "f"(v), "n"(1u << SHIFT));
 }
 
 // Bit position of coordinate k of a packed 32-bit word (MSB-first within bytes).
@@ -143,17 +150,15 @@ template <int BITS> __device__ __forceinline__ uint32_t index_shift(int k) {
   return BITS == 4 ? (uint32_t)(8 * (k >> 1) + ((k & 1) ? 0 : 4)) : (uint32_t)(8 * (k >> 2) + (6 - 2 * (k & 3)));
 }
 
-// Two IEEE round-to-nearest FP32 operations per instruction (sm_100 f32x2).
+// Two IEEE round-to-nearest FP32 operations per instruction (sm_100 f32x2, through
+// the float2 intrinsics so that the compiler keeps the pairs in aligned registers).
 // Each half is rounded exactly like the scalar operation, so results are
 // bit-identical to upstream's scalar code; only the issue slots are halved.
-__device__ __forceinline__ unsigned long long pack2(float a, float b) {
-  unsigned long long r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long v, float &a, float &b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
+__device__ __forceinline__ float2 mulp(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 addp(float2 a, float2 b) { return __fadd2_rn(a, b); }
+// a - b as b * (-1) + a: the product is exact, so this rounds once, like the subtraction
+__device__ __forceinline__ float2 subp(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a); }
+__device__ __forceinline__ float2 fmap(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 
 // ---------------------------------------------------------------------------
 // General routine: one warp per vector, the vector lives in shared memory
@@ -275,7 +280,10 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) append_general_kernel(const Ap
 #endif
 constexpr int AT_TILE = AQ_AT_TILE;          // vectors per tile
 constexpr int AT_THREADS = 4 * AT_TILE;      // four lanes per vector
-constexpr int AT_BLOCKS_PER_SM = 1024 / AT_THREADS;
+#ifndef AQ_AT_BPS
+#define AQ_AT_BPS (1024 / (4 * AQ_AT_TILE))
+#endif
+constexpr int AT_BLOCKS_PER_SM = AQ_AT_BPS;
 
 template <int NBYTES> __device__ __forceinline__ void store_packed(uint8_t *dst, const uint32_t *w) {
   if constexpr (NBYTES == 16) {
@@ -294,26 +302,13 @@ template <int NBYTES> __device__ __forceinline__ void store_packed(uint8_t *dst,
   }
 }
 
-// Packed-pair helpers: a 64-bit register pair holds coordinates (2i, 2i+1).
-__device__ __forceinline__ unsigned long long mulp(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ unsigned long long addp(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ unsigned long long subp(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ unsigned long long fmap(unsigned long long a, unsigned long long b, unsigned long long c) {
-  unsigned long long r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
+// One packed 32-bit word from 32/BITS consecutive coordinates (shifts unrolled at compile time).
+template <int BITS, int K> __device__ __forceinline__ void quantize_word(uint32_t &word, const float *x, uint32_t qtab_addr) {
+  if constexpr (K < 32 / BITS) {
+    constexpr uint32_t SH = BITS == 4 ? (uint32_t)(8 * (K >> 1) + ((K & 1) ? 0 : 4)) : (uint32_t)(8 * (K >> 2) + (6 - 2 * (K & 3)));
+    quantize_into_word<BITS, SH>(word, x[K], qtab_addr);
+    quantize_word<BITS, K + 1>(word, x, qtab_addr);
+  }
 }
 
 // Quarter-vector transform + quantisation.  xp: this lane's EPL = P/4 contiguous
@@ -321,20 +316,19 @@ __device__ __forceinline__ unsigned long long fmap(unsigned long long a, unsigne
 // instructions need no register shuffling), sgw = the sign bits of those
 // coordinates in bits 0..EPL-1.  Produces EPL*BITS/8 packed bytes in w.
 template <int P, int BITS>
-__device__ __forceinline__ void quantize_quarter(unsigned long long (&xp)[P / 8], float inv, float sq, float isq,
+__device__ __forceinline__ void quantize_quarter(float2 (&xp)[P / 8], float inv, float sq, float isq,
                                                  uint32_t sgw, int lane, uint32_t (&w)[(P / 4 * BITS + 31) / 32],
                                                  uint32_t qtab_addr) {
   constexpr int EPL = P / 4, NP = EPL / 2;
-  const unsigned long long inv2 = pack2(inv, inv);
+  const float2 inv2 = make_float2(inv, inv);
   // normalise, Rademacher sign (a sign-bit XOR equals the multiply by +-1), and the
   // len = 1 stage, which pairs the two halves of a register pair (core/fwht.cpp:36-42)
 #pragma unroll
   for (int i = 0; i < NP; ++i) {
-    float a, b;
-    unpack2(mulp(xp[i], inv2), a, b);
-    a = __uint_as_float(__float_as_uint(a) ^ ((sgw << (31 - 2 * i)) & 0x80000000u));
-    b = __uint_as_float(__float_as_uint(b) ^ ((sgw << (30 - 2 * i)) & 0x80000000u));
-    xp[i] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));
+    const float2 n = mulp(xp[i], inv2);
+    const float a = __uint_as_float(__float_as_uint(n.x) ^ ((sgw << (31 - 2 * i)) & 0x80000000u));
+    const float b = __uint_as_float(__float_as_uint(n.y) ^ ((sgw << (30 - 2 * i)) & 0x80000000u));
+    xp[i] = make_float2(__fadd_rn(a, b), __fsub_rn(a, b));
   }
   // stages len = 2 .. EPL/2 stay inside the lane: pairs at distance len/2
 #pragma unroll
@@ -343,7 +337,7 @@ __device__ __forceinline__ void quantize_quarter(unsigned long long (&xp)[P / 8]
     for (int i = 0; i < NP; i += (hl << 1)) {
 #pragma unroll
       for (int j = 0; j < hl; ++j) {
-        const unsigned long long lo = xp[i + j], hi = xp[i + j + hl];
+        const float2 lo = xp[i + j], hi = xp[i + j + hl];
         xp[i + j] = addp(lo, hi);
         xp[i + j + hl] = subp(lo, hi);
       }
@@ -355,22 +349,40 @@ __device__ __forceinline__ void quantize_quarter(unsigned long long (&xp)[P / 8]
 #pragma unroll
   for (int m = 8; m <= 16; m <<= 1) {
     const float sgn = (lane & m) ? -1.0f : 1.0f;
-    const unsigned long long sgn2 = pack2(sgn, sgn);
+    const float2 sgn2 = make_float2(sgn, sgn);
 #pragma unroll
-    for (int i = 0; i < NP; ++i) xp[i] = fmap(xp[i], sgn2, __shfl_xor_sync(0xffffffffu, xp[i], m));
+    for (int i = 0; i < NP; ++i) {
+      const float2 other = make_float2(__shfl_xor_sync(0xffffffffu, xp[i].x, m), __shfl_xor_sync(0xffffffffu, xp[i].y, m));
+      xp[i] = fmap(xp[i], sgn2, other);
+    }
   }
   // x * (1/sqrt p) [core/fwht.cpp:60-65]  then * sqrt p [core/quantizer.cpp:73-75]
-  const unsigned long long sq2 = pack2(sq, sq), isq2 = pack2(isq, isq);
+  const float2 sq2 = make_float2(sq, sq), isq2 = make_float2(isq, isq);
   float x[EPL];
 #pragma unroll
-  for (int i = 0; i < NP; ++i) unpack2(mulp(mulp(xp[i], isq2), sq2), x[2 * i], x[2 * i + 1]);
+  for (int i = 0; i < NP; ++i) {
+    const float2 v = mulp(mulp(xp[i], isq2), sq2);
+    x[2 * i] = v.x;
+    x[2 * i + 1] = v.y;
+  }
   if constexpr (BITS == 3) { // 8 indices -> 3 bytes, big-endian bit order
     uint32_t r[EPL / 8];
 #pragma unroll
     for (int g = 0; g < EPL / 8; ++g) {
       uint32_t v24 = 0;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v24 += quantize_lookup<3>(x[g * 8 + k], qtab_addr) << (21 - 3 * k);
+      for (int k = 0; k < 8; ++k) {
+        switch (k) { // the shift must be a compile-time constant
+        case 0: quantize_into_word<3, 21>(v24, x[g * 8 + 0], qtab_addr); break;
+        case 1: quantize_into_word<3, 18>(v24, x[g * 8 + 1], qtab_addr); break;
+        case 2: quantize_into_word<3, 15>(v24, x[g * 8 + 2], qtab_addr); break;
+        case 3: quantize_into_word<3, 12>(v24, x[g * 8 + 3], qtab_addr); break;
+        case 4: quantize_into_word<3, 9>(v24, x[g * 8 + 4], qtab_addr); break;
+        case 5: quantize_into_word<3, 6>(v24, x[g * 8 + 5], qtab_addr); break;
+        case 6: quantize_into_word<3, 3>(v24, x[g * 8 + 6], qtab_addr); break;
+        default: quantize_into_word<3, 0>(v24, x[g * 8 + 7], qtab_addr); break;
+        }
+      }
       r[g] = __byte_perm(v24, 0, 0x3012); // memory image of the three bytes, first byte lowest
     }
     if constexpr (EPL == 32) {
@@ -386,8 +398,7 @@ __device__ __forceinline__ void quantize_quarter(unsigned long long (&xp)[P / 8]
 #pragma unroll
     for (int i = 0; i < EPL; i += PER) {
       uint32_t word = 0;
-#pragma unroll
-      for (int k = 0; k < PER; ++k) word += quantize_lookup<BITS>(x[i + k], qtab_addr) << index_shift<BITS>(k);
+      quantize_word<BITS, 0>(word, x + i, qtab_addr);
       w[i / PER] = word;
     }
   }
@@ -486,20 +497,19 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const fl
       bool live = false;
       if (g < n_items) live = place_item32(a, (uint32_t)g).store;
       if (live) {
-        const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(row_ptr(row1));
+        const float4 *r4 = reinterpret_cast<const float4 *>(row_ptr(row1));
         float sum = 0.f;
 #pragma unroll 8
         for (int i = 0; i < P / 4; ++i) {
-          const ulonglong2 v = r2[i];
-          float s0, s1, s2, s3;
-          unpack2(mulp(v.x, v.x), s0, s1);
-          unpack2(mulp(v.y, v.y), s2, s3);
-          sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, s0), s1), s2), s3);
+          const float4 v = r4[i];
+          const float2 s01 = mulp(make_float2(v.x, v.y), make_float2(v.x, v.y));
+          const float2 s23 = mulp(make_float2(v.z, v.w), make_float2(v.z, v.w));
+          sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, s01.x), s01.y), s23.x), s23.y);
         }
         const bool all_zero = sum == 0.f;
         const float norm = __fsqrt_rn(__fadd_rn(sum, 1e-12f));
         // norm >= 1e-5 makes the +-3 sigma clip a no-op and rules out NaN (see
-        // quantize_lookup); an all-zero vector quantises to the middle index either way
+        // quantize_into_word); an all-zero vector quantises to the middle index either way
         const bool plain = (norm >= 1e-5f && norm < INFINITY) || all_zero;
         s_norm[row1] = plain ? make_float2(norm, __fdiv_rn(1.0f, norm)) : make_float2(-1.f, 1.f);
         if (!plain) redo_list[par][atomicAdd(&redo_count[par], 1)] = row1;
@@ -535,15 +545,20 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const fl
     if (skip) p.store = p.mirror = false;
     if ((p.store || p.mirror) && !AQ_CHECK(a.status, p.slot >= 0 && p.slot < c.cap && p.h >= 0 && p.h < c.n_heads, 11))
       p.store = p.mirror = false;
-    unsigned long long xp[EPL / 2]; // coordinates (2i, 2i+1) of this quarter, packed
+    float2 xp[EPL / 2]; // coordinates (2i, 2i+1) of this quarter, packed
     {
       const bool have = p.store || p.mirror;
-      const ulonglong2 *r2 = reinterpret_cast<const ulonglong2 *>(row_ptr(vt) + part * EPL);
+      const float4 *r4 = reinterpret_cast<const float4 *>(row_ptr(vt) + part * EPL);
+      if (have) {
 #pragma unroll
-      for (int i = 0; i < EPL / 4; ++i) {
-        const ulonglong2 v = have ? r2[i] : make_ulonglong2(0ull, 0ull);
-        xp[2 * i] = v.x;
-        xp[2 * i + 1] = v.y;
+        for (int i = 0; i < EPL / 4; ++i) {
+          const float4 v = r4[i];
+          xp[2 * i] = make_float2(v.x, v.y);
+          xp[2 * i + 1] = make_float2(v.z, v.w);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < EPL / 2; ++i) xp[i] = make_float2(0.f, 0.f);
       }
     }
     __syncthreads(); // every quarter is in registers; the tile buffer is free
@@ -553,19 +568,19 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const fl
       issue(next);
     }
     if (p.mirror) {
-      ulonglong2 *m2 = reinterpret_cast<ulonglong2 *>(c.mirror + (size_t)p.h * c.mirror_stride +
-                                                      (size_t)p.slot * 2 * dim + (which ? dim : 0) + part * EPL);
+      float4 *m4 = reinterpret_cast<float4 *>(c.mirror + (size_t)p.h * c.mirror_stride +
+                                              (size_t)p.slot * 2 * dim + (which ? dim : 0) + part * EPL);
 #pragma unroll
       for (int i = 0; i < EPL / 4; ++i)
-        if (part * EPL + 4 * i < dim) m2[i] = make_ulonglong2(xp[2 * i], xp[2 * i + 1]);
+        if (part * EPL + 4 * i < dim) m4[i] = make_float4(xp[2 * i].x, xp[2 * i].y, xp[2 * i + 1].x, xp[2 * i + 1].y);
     }
     if constexpr (BITS == 16) {
       if (p.store) {
         uint8_t *slab = which ? c.v_slab : c.k_slab;
         const size_t stride = which ? c.v_stride : c.k_stride;
-        ulonglong2 *dst = reinterpret_cast<ulonglong2 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4)) + part * (EPL / 4);
+        float4 *dst = reinterpret_cast<float4 *>(slab + (size_t)p.h * stride + (size_t)p.slot * (P * 4)) + part * (EPL / 4);
 #pragma unroll
-        for (int i = 0; i < EPL / 4; ++i) dst[i] = make_ulonglong2(xp[2 * i], xp[2 * i + 1]);
+        for (int i = 0; i < EPL / 4; ++i) dst[i] = make_float4(xp[2 * i].x, xp[2 * i].y, xp[2 * i + 1].x, xp[2 * i + 1].y);
         if (part == 0) ((which ? c.v_scale : c.k_scale) + (size_t)p.h * c.s_stride)[p.slot] = 1.0f;
       }
     } else {

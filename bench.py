@@ -482,6 +482,17 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
         parts = torch.empty((world, H, 1, 2 + D), device="cuda")
 
         pg = None
+        if exchange == "peer" and dist is None:
+            # one rank: the same two kernels with this GPU's own buffers as the only "peer"
+            class _Local:
+                pass
+            pg = _Local()
+            n_buf = H * (2 + D)
+            pg._t = torch.zeros(2 * n_buf + 64, dtype=torch.float32, device="cuda")
+            pg.items, pg.step = H, 0
+            base = pg._t.data_ptr()
+            pg.buf_ptrs = [[base + 4 * par * n_buf] for par in (0, 1)]
+            pg.flag_ptrs = [base + 8 * n_buf]
         if exchange == "peer" and dist is not None:
             from adaptq_b200.sharded import PeerGather
             ok = torch.ones(1, device="cuda")
@@ -545,7 +556,7 @@ def longctx_bench(torch, dist, world, rank, steps, warmup, peak, exchange="nccl"
         alg = H * (N * (D * kb // 8 + D * vb // 8 + 8) + 8 * D)
         us_total = timed(step_sharded)
         us_local = timed(step_local)
-        res = {"exchange": "none" if dist is None else ("peer" if pg is not None else "nccl"), "us_per_step": us_total, "us_local_kernels": us_local, "us_gather_and_merge": us_total - us_local,
+        res = {"exchange": ("peer" if pg is not None else "nccl") if (dist is not None or pg is not None) else "none", "us_per_step": us_total, "us_local_kernels": us_local, "us_gather_and_merge": us_total - us_local,
                "effective_kv_gbs_all_ranks": alg / us_total / 1e3, "local_kernel_gbs_per_gpu": alg / world / us_local / 1e3,
                "local_kernel_frac_of_peak": alg / world / us_local / 1e3 / peak,
                "algorithmic_bytes": alg, "tokens_per_rank": local_n}

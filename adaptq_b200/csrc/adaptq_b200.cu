@@ -571,10 +571,29 @@ bool append_device(Group *g, const float *dk, const float *dv, int head0, int he
 // ---------------------------------------------------------------------------
 size_t partial_floats(const CacheView &c) { return (size_t)2 + c.padded; }
 
-// The general kernel's dynamic shared memory limit only ever grows (per device).
-bool ensure_general_smem(Group *g, size_t smem) {
+// The general kernel's dynamic shared memory limit only ever grows (per device and variant).
+template <bool KW, bool VW>
+bool launch_general_variant(Group *g, const ComputeLaunch &a, dim3 grid, size_t smem, const char *what) {
   static int smem_set[MAX_DEVICES] = {};
-  return ensure_smem_limit(compute_general_kernel, smem_set, g->device, smem, "compute");
+  auto kern = compute_general_kernel<KW, VW>;
+  if (!ensure_smem_limit(kern, smem_set, g->device, smem, what)) return false;
+  kern<<<grid, CG_THREADS, smem, g->stream>>>(a);
+  ++g_launches;
+  CUDA_TRY(launch_status(), what);
+  return true;
+}
+
+// Packed rows are read by words where they are whole words (padded dimension a multiple of 32).
+bool general_by_words(const CacheView &c, bool side_f32) { return !side_f32 && c.padded % 32 == 0; }
+
+// Tokens per shared-memory pass; the by-words fold of V needs 8 rows of the padded dimension there.
+int general_chunk(const CacheView &c, int span, bool vw) {
+  return std::max(std::max(CG_THREADS, std::min(span, 2048)), vw ? 8 * c.padded : 0);
+}
+
+bool launch_general_kernel(Group *g, const ComputeLaunch &a, dim3 grid, size_t smem, bool kw, bool vw, const char *what) {
+  if (kw) return vw ? launch_general_variant<true, true>(g, a, grid, smem, what) : launch_general_variant<true, false>(g, a, grid, smem, what);
+  return vw ? launch_general_variant<false, true>(g, a, grid, smem, what) : launch_general_variant<false, false>(g, a, grid, smem, what);
 }
 
 bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *partial_out) {
@@ -588,10 +607,10 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   a.n_splits = std::min(want, max_splits);
   a.span = (int)round_up((size_t)(a.n + a.n_splits - 1) / a.n_splits, 32);
   a.n_splits = (a.n + a.span - 1) / a.span;
+  const bool kw = general_by_words(c, k_f32), vw = general_by_words(c, v_f32);
   a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
   const int kcb = k_f32 ? 0 : (1 << c.k_bits);
-  size_t smem = cg_smem_floats(c.padded, kcb, a.chunk) * sizeof(float);
-  if (!ensure_general_smem(g, smem)) return false;
+  size_t smem = cg_smem_floats(c.padded, kcb, general_chunk(c, a.span, vw)) * sizeof(float);
   const bool direct = a.n_splits == 1 && !want_partial_out;
   if (!direct) {
     if (!ensure_scratch(g, (size_t)a.n_splits * items * partial_floats(c) * sizeof(float))) return false;
@@ -606,9 +625,7 @@ bool launch_general(Group *g, ComputeLaunch &a, bool want_partial_out, float *pa
   a.final_out = want_partial_out ? partial_out : a.out;
   a.final_to_partial = want_partial_out ? 1 : 0;
   dim3 grid(a.n_splits, a.heads_in_call, a.nq);
-  compute_general_kernel<<<grid, CG_THREADS, smem, g->stream>>>(a);
-  ++g_launches;
-  CUDA_TRY(launch_status(), "compute");
+  if (!launch_general_kernel(g, a, grid, smem, kw, vw, "compute")) return false;
   if (!direct && !fused) {
     merge_partials_kernel<<<items, CG_THREADS, c.padded * sizeof(float), g->stream>>>(
         a.partial, (size_t)items * partial_floats(c), a.n_splits, c, a.head0, a.nq,
@@ -629,16 +646,13 @@ bool launch_logits(Group *g, ComputeLaunch &a, float *w, int ws) {
   a.n_splits = (a.n + a.span - 1) / a.span;
   a.chunk = std::max(CG_THREADS, std::min(a.span, 2048));
   size_t smem = cg_smem_floats(c.padded, 1 << c.k_bits, a.chunk) * sizeof(float);
-  if (!ensure_general_smem(g, smem)) return false;
-  compute_general_kernel<<<dim3(a.n_splits, a.heads_in_call, a.nq), CG_THREADS, smem, g->stream>>>(a);
-  ++g_launches;
-  CUDA_TRY(launch_status(), "compute (logits)");
-  return true;
+  return launch_general_kernel(g, a, dim3(a.n_splits, a.heads_in_call, a.nq), smem, general_by_words(c, false), false,
+                               "compute (logits)");
 }
 
 template <int ITEMS>
 bool launch_sparse_fused_t(Group *g, const ComputeLaunch &a, const float *w, int ws) {
-  const size_t smem = SparseSmem<ITEMS>::bytes;
+  const size_t smem = SparseSmem<ITEMS>::bytes + sparse_fold_bytes(g->c.padded, g->c.v_bits);
   static int configured[MAX_DEVICES] = {};
   auto kern = sparse_fused_kernel<ITEMS>;
   if (!ensure_smem_limit(kern, configured, g->device, smem, "compute (sparse V)")) return false;

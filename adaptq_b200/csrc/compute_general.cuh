@@ -40,9 +40,105 @@ struct ComputeLaunch {
   int final_to_partial;
 };
 
-// Shared-memory carve-up (floats): qr[P] | vec[P] | red[64] | lut[P*CBK or 0] | sc[chunk]
+// Shared-memory carve-up (floats): qr[P] | vec[P] | red[64] | vcb[16] | lut[P*CBK or 0] | sc[chunk]
 __host__ __device__ inline size_t cg_smem_floats(int P, int k_quant_levels, int chunk) {
-  return (size_t)P * 2 + 64 + (size_t)P * k_quant_levels + chunk;
+  return (size_t)P * 2 + 64 + 16 + (size_t)P * k_quant_levels + chunk;
+}
+
+// ---- packed rows by words -------------------------------------------------------------------
+// For padded dimensions that are multiples of 32 a packed row is a whole number of 32-bit
+// words, and 32 consecutive coordinates fill exactly BITS words.  Read as big-endian words the
+// MSB-first layouts of upstream's packers (core/quantizer.cpp:156-194) become one bit stream:
+// coordinate k of a 32-coordinate group starts k*BITS bits below the top of its first word.
+template <int WORDS> __device__ __forceinline__ void load_words_be(const uint8_t *p, uint32_t (&w)[WORDS]) {
+  if constexpr (WORDS == 4) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else if constexpr (WORDS == 2) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
+    w[0] = v.x; w[1] = v.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < WORDS; ++i) w[i] = __ldg(reinterpret_cast<const uint32_t *>(p) + i);
+  }
+#pragma unroll
+  for (int i = 0; i < WORDS; ++i) w[i] = __byte_perm(w[i], 0, 0x0123);
+}
+
+// level of coordinate k (k*BITS bits from the top of w[0]); k is a constant after unrolling
+template <int BITS, int WORDS> __device__ __forceinline__ uint32_t level_of(const uint32_t (&w)[WORDS], int k) {
+  const int o = k * BITS, wi = o >> 5, sh = o & 31;
+  if (sh + BITS <= 32) return (w[wi] >> (32 - BITS - sh)) & ((1u << BITS) - 1u);
+  return __funnelshift_l(w[wi + 1 < WORDS ? wi + 1 : wi], w[wi], sh) >> (32 - BITS);
+}
+
+// One thread scores one packed K row against the table lut[j * 2^BITS + level]: the lanes of
+// a warp read the same j with their own levels, i.e. words of one 2^BITS-word segment, which
+// never collide in a bank.
+template <int BITS> __device__ __forceinline__ float score_row_words(const uint8_t *kr, const float *lut, int P) {
+  constexpr int L = 1 << BITS;
+  float s0 = 0.f, s1 = 0.f;
+  for (int g = 0; g < P / 32; ++g) {
+    uint32_t w[BITS];
+    load_words_be<BITS>(kr + g * 4 * BITS, w);
+    const float *lt = lut + (size_t)g * 32 * L;
+#pragma unroll
+    for (int k = 0; k < 32; k += 2) {
+      s0 += lt[k * L + level_of<BITS, BITS>(w, k)];
+      s1 += lt[(k + 1) * L + level_of<BITS, BITS>(w, k + 1)];
+    }
+  }
+  return s0 + s1;
+}
+
+// V rows by words: a thread owns one unit of a row (one word at 2 or 4 bits, three words = 32
+// coordinates at 3 bits) for every token of its token group.
+template <int BITS> struct VUnit {
+  static constexpr int WORDS = BITS == 3 ? 3 : 1;
+  static constexpr int NCO = WORDS * 32 / BITS; // coordinates per unit: 16 / 32 / 8
+};
+
+template <int BITS>
+__device__ __forceinline__ void v_accumulate_words(float *acc, float rescale, const uint8_t *vunit, int v_row, const float *sc, int cn,
+                                                   int tg, int TG, const float *s_cb) {
+  using U = VUnit<BITS>;
+#pragma unroll
+  for (int k = 0; k < U::NCO; ++k) acc[k] *= rescale;
+#pragma unroll 2
+  for (int i = tg; i < cn; i += TG) {
+    uint32_t w[U::WORDS];
+    load_words_be<U::WORDS>(vunit + (size_t)i * v_row, w);
+    const float wt = sc[i];
+#pragma unroll
+    for (int k = 0; k < U::NCO; ++k) acc[k] += wt * s_cb[level_of<BITS, U::WORDS>(w, k)];
+  }
+}
+
+// Sum the token groups' accumulators into vec[P]: lanes that hold the same unit first (shuffles),
+// then one row per warp (or per token group when a row has more than 32 units) through `buf`.
+template <int BITS, int THREADS> __device__ __forceinline__ void v_fold_words(float *acc, int P, float *buf, float *vec) {
+  using UU = VUnit<BITS>;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int U = P / UU::NCO; // units per row, a power of two
+  if (U < 32) {
+    for (int off = U; off < 32; off <<= 1) {
+#pragma unroll
+      for (int k = 0; k < UU::NCO; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], off);
+    }
+  }
+  const int rows = U <= 32 ? THREADS / 32 : THREADS / U;
+  const int row = U <= 32 ? warp : tid / U;
+  const int u = tid % U;
+  if (U >= 32 || lane < U) {
+#pragma unroll
+    for (int k = 0; k < UU::NCO; ++k) buf[(size_t)row * P + u * UU::NCO + k] = acc[k];
+  }
+  __syncthreads();
+  for (int j = tid; j < P; j += THREADS) {
+    float t = 0.f;
+    for (int r = 0; r < rows; ++r) t += buf[(size_t)r * P + j];
+    vec[j] = t;
+  }
 }
 
 __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) {
@@ -168,8 +264,11 @@ __global__ void __launch_bounds__(CG_THREADS) merge_partials_kernel(
                        reinterpret_cast<float *>(smem_gen), guard_n);
 }
 
+// KW / VW: the packed keys / values are read by words (quantised, padded dimension a multiple
+// of 32); otherwise by bytes or as floats.
+template <bool KW, bool VW>
 __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const ComputeLaunch a) {
-  extern __shared__ __align__(16) unsigned char smem_gen[];
+  extern __shared__ __align__(128) unsigned char smem_gen[];
   unsigned char *smem_raw = smem_gen;
   const CacheView &c = a.c;
   const int P = c.padded, dim = c.dim;
@@ -185,7 +284,8 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   float *qr = reinterpret_cast<float *>(smem_raw);
   float *vec = qr + P;
   float *red = vec + P;
-  float *lut = red + 64;
+  float *s_vcb = red + 64;
+  float *lut = s_vcb + 16;
   float *sc = lut + (size_t)P * kcb;
 
   const float *q = a.q + ((size_t)hl * a.nq + qi) * dim;
@@ -208,10 +308,17 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
     for (int i = tid; i < P; i += CG_THREADS) qr[i] = qr[i] * isp * m;
     __syncthreads();
     attn_s = 1.f / (sqrtf((float)dim) * (float)P);
-    // table[level][j] = q_rot[j] * centroid[level]; column j sits in bank j%32
     const float *cb = c_cb[c.k_bits - 2];
-    for (int i = tid; i < P * kcb; i += CG_THREADS) lut[i] = qr[i % P] * cb[i / P];
+    if constexpr (KW) { // table[j][level]: a warp's lanes (one token each) read one segment per j
+      for (int i = tid; i < P * kcb; i += CG_THREADS) lut[i] = qr[i / kcb] * cb[i % kcb];
+    } else { // table[level][j] = q_rot[j] * centroid[level]; column j sits in bank j%32
+      for (int i = tid; i < P * kcb; i += CG_THREADS) lut[i] = qr[i % P] * cb[i / P];
+    }
     __syncthreads();
+  }
+  if constexpr (VW) {
+    if (tid < 16) s_vcb[tid] = tid < (1 << c.v_bits) ? c_cb[c.v_bits - 2][tid] : 0.f;
+    // visible after the first barrier of the token loop
   }
 
   const uint8_t *kbase = c.k_slab + (size_t)h * c.k_stride;
@@ -229,6 +336,12 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   const int tg = P < CG_THREADS ? tid / P : 0;
   constexpr int MAXR = 4; // P <= 1024
   float acc[MAXR] = {0.f, 0.f, 0.f, 0.f};
+  // by words: unit vu of token group vtg, up to 32 coordinates per thread
+  float accw[VW ? 32 : 1];
+#pragma unroll
+  for (int k = 0; k < (VW ? 32 : 1); ++k) accw[k] = 0.f;
+  const int v_nco = c.v_bits == 2 ? 16 : c.v_bits == 3 ? 32 : 8;
+  const int VU = VW ? P / v_nco : 1, vu = tid % VU, vtg = tid / VU, VTG = CG_THREADS / VU;
   // the running maximum starts where upstream's does (attention.cpp:384, :498, :566): logits
   // below it (or NaN) never become the maximum, and their weights come out as upstream's do
   float run_m = -1e30f, run_l = 0.f;
@@ -237,19 +350,29 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   for (int t0 = t_begin; t0 < t_end; t0 += a.chunk) {
     const int cn = min(a.chunk, t_end - t0);
     // ---- scores ----------------------------------------------------------
-#pragma unroll 4
-    for (int i = warp; i < cn; i += CG_WARPS) {
-      const int s = t0 + i;
-      float sum = 0.f;
-      if (k_f32) {
-        const float *kr = mirror ? mir + (size_t)s * 2 * dim : reinterpret_cast<const float *>(kbase + (size_t)s * c.k_row);
-        for (int j = lane; j < dim; j += 32) sum += qr[j] * kr[j];
-      } else {
+    if constexpr (KW) {
+      for (int i = tid; i < cn; i += CG_THREADS) {
+        const int s = t0 + i;
         const uint8_t *kr = kbase + (size_t)s * c.k_row;
-        for (int j = lane; j < P; j += 32) sum += lut[unpack_at(kr, j, c.k_bits) * P + j];
+        const float sum = c.k_bits == 4 ? score_row_words<4>(kr, lut, P)
+                          : c.k_bits == 3 ? score_row_words<3>(kr, lut, P) : score_row_words<2>(kr, lut, P);
+        sc[i] = sum * attn_s * ksc[s];
       }
-      sum = warp_sum(sum);
-      if (lane == 0) sc[i] = k_f32 ? sum * attn_s : sum * attn_s * ksc[s];
+    } else {
+#pragma unroll 4
+      for (int i = warp; i < cn; i += CG_WARPS) {
+        const int s = t0 + i;
+        float sum = 0.f;
+        if (k_f32) {
+          const float *kr = mirror ? mir + (size_t)s * 2 * dim : reinterpret_cast<const float *>(kbase + (size_t)s * c.k_row);
+          for (int j = lane; j < dim; j += 32) sum += qr[j] * kr[j];
+        } else {
+          const uint8_t *kr = kbase + (size_t)s * c.k_row;
+          for (int j = lane; j < P; j += 32) sum += lut[unpack_at(kr, j, c.k_bits) * P + j];
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) sc[i] = k_f32 ? sum * attn_s : sum * attn_s * ksc[s];
+      }
     }
     __syncthreads();
     if (a.mode == 2) { // raw logits out, stored by LOGICAL position (oldest token first, as upstream
@@ -281,24 +404,31 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
     run_m = new_m;
     __syncthreads();
     // ---- V accumulation ------------------------------------------------------
+    if constexpr (VW) {
+      const uint8_t *vunit = vbase + (size_t)t0 * c.v_row + (size_t)vu * (c.v_bits == 3 ? 12 : 4);
+      if (c.v_bits == 2) v_accumulate_words<2>(accw, rescale, vunit, c.v_row, sc, cn, vtg, VTG, s_vcb);
+      else if (c.v_bits == 3) v_accumulate_words<3>(accw, rescale, vunit, c.v_row, sc, cn, vtg, VTG, s_vcb);
+      else v_accumulate_words<4>(accw, rescale, vunit, c.v_row, sc, cn, vtg, VTG, s_vcb);
+    } else {
 #pragma unroll
-    for (int r = 0; r < MAXR; ++r) {
-      const int j = jcol + r * CG_THREADS;
-      if (j >= P || (P < CG_THREADS && r > 0)) break;
-      float av = acc[r] * rescale;
+      for (int r = 0; r < MAXR; ++r) {
+        const int j = jcol + r * CG_THREADS;
+        if (j >= P || (P < CG_THREADS && r > 0)) break;
+        float av = acc[r] * rescale;
 #pragma unroll 4
-      for (int i = tg; i < cn; i += TG) {
-        const int s = t0 + i;
-        if (v_f32) {
-          if (j < dim) {
-            const float *vr = mirror ? mir + (size_t)s * 2 * dim + dim : reinterpret_cast<const float *>(vbase + (size_t)s * c.v_row);
-            av += sc[i] * vr[j];
+        for (int i = tg; i < cn; i += TG) {
+          const int s = t0 + i;
+          if (v_f32) {
+            if (j < dim) {
+              const float *vr = mirror ? mir + (size_t)s * 2 * dim + dim : reinterpret_cast<const float *>(vbase + (size_t)s * c.v_row);
+              av += sc[i] * vr[j];
+            }
+          } else {
+            av += sc[i] * vcb[unpack_at(vbase + (size_t)s * c.v_row, j, c.v_bits)];
           }
-        } else {
-          av += sc[i] * vcb[unpack_at(vbase + (size_t)s * c.v_row, j, c.v_bits)];
         }
+        acc[r] = av;
       }
-      acc[r] = av;
     }
     __syncthreads();
   }
@@ -306,7 +436,11 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
 
   // ---- fold token groups ------------------------------------------------------
   // vec[j] = sum over token groups; TG groups of P columns fit CG_THREADS exactly
-  if (P < CG_THREADS) {
+  if constexpr (VW) { // sc holds at least 8*P floats (the host sizes it)
+    if (c.v_bits == 2) v_fold_words<2, CG_THREADS>(accw, P, sc, vec);
+    else if (c.v_bits == 3) v_fold_words<3, CG_THREADS>(accw, P, sc, vec);
+    else v_fold_words<4, CG_THREADS>(accw, P, sc, vec);
+  } else if (P < CG_THREADS) {
     float *fold = sc; // chunk >= CG_THREADS floats is guaranteed by the host
     fold[tid] = acc[0];
     __syncthreads();

@@ -30,8 +30,17 @@ template <int ITEMS> struct SparseSmem {
   // sort scratch (later reused for the block sums and the group fold) | weights | tokens | vec[1024] | red[64]
   static constexpr size_t sort_bytes = (sizeof(typename Sort::TempStorage) + 15) / 16 * 16;
   static constexpr size_t scratch_bytes = sort_bytes > (size_t)CAP ? sort_bytes : (size_t)CAP; // >= CAP/4 floats and >= SP_THREADS floats
-  static constexpr size_t bytes = scratch_bytes + (size_t)CAP * 8 + 1024 * 4 + 64 * 4;
+  static constexpr size_t bytes = scratch_bytes + (size_t)CAP * 8 + 1024 * 4 + 64 * 4; // a multiple of 16
 };
+
+// Bytes of the by-words fold: one row of P floats per warp, or per token group when a packed
+// row has more than 32 units.
+inline size_t sparse_fold_bytes(int P, int v_bits) {
+  if (P % 32 != 0) return 0;
+  const int units = P / (v_bits == 2 ? 16 : v_bits == 3 ? 32 : 8);
+  const int rows = units <= 32 ? SP_THREADS / 32 : SP_THREADS / units;
+  return (size_t)rows * P * sizeof(float);
+}
 
 __device__ __forceinline__ float sp_block_reduce(float v, float *red, bool is_max) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -42,6 +51,31 @@ __device__ __forceinline__ float sp_block_reduce(float v, float *red, bool is_ma
   float r = red[0];
   for (int i = 1; i < SP_THREADS / 32; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
   return r;
+}
+
+// V rows of the first `count` sorted tokens, by words (padded dimension a multiple of 32):
+// s_w[i] already holds w * vscale / sqrt(p).  `buf` takes sparse_fold_bytes() for the fold.
+template <int BITS>
+__device__ __forceinline__ void sparse_v_words(const float *s_w, const int *s_tok, int count, const uint8_t *vbase, const CacheView &c,
+                                               const float *s_cb, float *buf, float *vec, int *status) {
+  using UU = VUnit<BITS>;
+  const int tid = threadIdx.x, P = c.padded;
+  const int U = P / UU::NCO, u = tid % U, tg = tid / U, TG = SP_THREADS / U;
+  float acc[UU::NCO];
+#pragma unroll
+  for (int k = 0; k < UU::NCO; ++k) acc[k] = 0.f;
+  const uint8_t *vunit = vbase + (size_t)u * (UU::WORDS * 4);
+#pragma unroll 2
+  for (int i = tg; i < count; i += TG) {
+    const int tok = s_tok[i];
+    if (!AQ_CHECK(status, tok >= 0 && tok < c.cap, 15)) continue;
+    uint32_t w[UU::WORDS];
+    load_words_be<UU::WORDS>(vunit + (size_t)tok * c.v_row, w);
+    const float wt = s_w[i];
+#pragma unroll
+    for (int k = 0; k < UU::NCO; ++k) acc[k] += wt * s_cb[level_of<BITS, UU::WORDS>(w, k)];
+  }
+  v_fold_words<BITS, SP_THREADS>(acc, P, buf, vec);
 }
 
 template <int ITEMS>
@@ -124,38 +158,36 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   for (int i = tid; i < count; i += SP_THREADS)
     if (AQ_CHECK(status, s_tok[i] >= 0 && s_tok[i] < c.cap, 15)) s_w[i] = s_w[i] * vsc[s_tok[i]] * isp;
   __syncthreads();
-  // ---- V rows of the chosen tokens: thread = (column, token group) ----------------------------
-  const int TG = P < SP_THREADS ? SP_THREADS / P : 1;
-  const int jcol = P < SP_THREADS ? tid % P : tid;
-  const int tg = P < SP_THREADS ? tid / P : 0;
-  constexpr int MAXR = 2; // P <= 1024
-  float acc[MAXR] = {0.f, 0.f};
-#pragma unroll
-  for (int r = 0; r < MAXR; ++r) {
-    const int j = jcol + r * SP_THREADS;
-    if (j >= P || (P < SP_THREADS && r > 0)) break;
+  // ---- V rows of the chosen tokens -------------------------------------------------------------
+  if (P % 32 == 0) {
+    // by words: thread = (unit of a row, token group); the units of a row are read side by side
+    float *s_cb = red + 32;
+    if (tid < 16) s_cb[tid] = tid < (1 << c.v_bits) ? vcb[tid] : 0.f;
+    __syncthreads();
+    float *fold = reinterpret_cast<float *>(smem_sp + S::bytes); // sparse_fold_bytes() behind the fixed part
+    if (c.v_bits == 2) sparse_v_words<2>(s_w, s_tok, count, vbase, c, s_cb, fold, vec, status);
+    else if (c.v_bits == 3) sparse_v_words<3>(s_w, s_tok, count, vbase, c, s_cb, fold, vec, status);
+    else sparse_v_words<4>(s_w, s_tok, count, vbase, c, s_cb, fold, vec, status);
+  } else {
+    // by bytes: thread = (column, token group)
+    const int TG = P < SP_THREADS ? SP_THREADS / P : 1;
+    const int jcol = P < SP_THREADS ? tid % P : tid;
+    const int tg = P < SP_THREADS ? tid / P : 0;
     float av = 0.f;
+    if (jcol < P) {
 #pragma unroll 4
-    for (int i = tg; i < count; i += TG) {
-      if (!AQ_CHECK(status, s_tok[i] >= 0 && s_tok[i] < c.cap, 15)) continue;
-      av += s_w[i] * vcb[unpack_at(vbase + (size_t)s_tok[i] * c.v_row, j, c.v_bits)];
+      for (int i = tg; i < count; i += TG) {
+        if (!AQ_CHECK(status, s_tok[i] >= 0 && s_tok[i] < c.cap, 15)) continue;
+        av += s_w[i] * vcb[unpack_at(vbase + (size_t)s_tok[i] * c.v_row, jcol, c.v_bits)];
+      }
     }
-    acc[r] = av;
-  }
-  __syncthreads(); // bsum is dead; reuse the scratch for the fold
-  if (P < SP_THREADS) {
-    scratch[tid] = acc[0];
+    __syncthreads(); // bsum is dead; reuse the scratch for the fold
+    scratch[tid] = av;
     __syncthreads();
     if (tid < P) {
       float t = 0.f;
       for (int g = 0; g < TG; ++g) t += scratch[g * P + tid];
       vec[tid] = t;
-    }
-  } else {
-#pragma unroll
-    for (int r = 0; r < MAXR; ++r) {
-      const int j = jcol + r * SP_THREADS;
-      if (j < P) vec[j] = acc[r];
     }
   }
   __syncthreads();

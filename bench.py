@@ -48,8 +48,8 @@ K_BITS, V_BITS = 4, 2
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) per algorithmic byte of the streaming decode kernel, from the ncu
 # capture summarised in profiles/compute_stream_kernel_k4v2_dim128_ctx8192.md (1024 heads:
-# 878.4 MB moved for 873.5 MB algorithmic); traffic grows in proportion to the heads processed.
-STREAM_TRAFFIC_PER_ALG_BYTE = 1.006
+# 877.1 MB moved for 873.5 MB algorithmic); traffic grows in proportion to the heads processed.
+STREAM_TRAFFIC_PER_ALG_BYTE = 1.004
 
 
 # The contract is ONE JSON line on stdout.  Libraries print there too (NCCL writes its

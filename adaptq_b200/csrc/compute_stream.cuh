@@ -1,5 +1,6 @@
 // Streaming split-KV decode-attention kernel for the bandwidth-bound shapes
-// (2- or 4-bit K and V at padded dimension 128; 4-bit K with 2- or 4-bit V at 64; dense V).
+// (2-, 3- or 4-bit K with 2- or 4-bit V at padded dimension 128; 3- or 4-bit K with 2- or
+// 4-bit V at 64; dense V).
 //
 // Replaces the same upstream code as compute_general.cuh -- the quantised
 // branch of AttentionHead::compute (attention/attention.cpp:526-563, :606-633)
@@ -18,7 +19,9 @@
 //    q_rot[coord]*centroid is built once per item; a score is the sum of one
 //    table entry per packed byte.  Lanes own byte columns so every table read
 //    is bank-conflict free, and the table sits on a 64 KB boundary so a
-//    single byte-permute forms the address;
+//    single byte-permute forms the address.  3-bit keys use 6-bit fields (two
+//    coordinates) in place of bytes: T[field value][field column], in four
+//    column-rotated copies so that the lanes of a warp step still read 32 banks;
 //  * the softmax is exact two-pass over the span (max, then exp), like
 //    upstream, with the scores held in shared memory;
 //  * V accumulation is the dual trick: instead of decoding V, the weight of a
@@ -187,16 +190,20 @@ __device__ __forceinline__ float quad_transpose_sum(float (&v)[STEPS], int wl) {
   }
 }
 
-// KB/VB: bits; KW/VW: 32-bit words per packed row (8 or 16).
+// KB/VB: bits; KW/VW: 32-bit words per packed row (8 or 16; 6 or 12 for 3-bit keys).
 template <int KB, int KW, int VB, int VW>
 __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const StreamLaunch a) {
   constexpr int P = KW * 32 / KB;
   static_assert(P == VW * 32 / VB, "K and V rows must describe the same padded dimension");
+  constexpr bool K3 = KB == 3;
+  static_assert(!K3 || KW == 6 || KW == 12, "3-bit keys: padded dimension 64 or 128");
   constexpr int KROW = KW * 4, VROW = VW * 4;
-  constexpr int TKN = CS_STAGE_BYTES / KROW, TVN = CS_STAGE_BYTES / VROW; // tokens per stage
+  // tokens per stage; 3-bit rows (24 or 48 bytes) fill 12 KB of a stage with a power of two of tokens
+  constexpr int TKN = K3 ? 12288 / KROW : CS_STAGE_BYTES / KROW, TVN = CS_STAGE_BYTES / VROW;
   // Lanes that share a token in the K stream: 4 with 32-byte rows, 8 with 64-byte rows
-  // (measured: fewer shuffles pay with the short rows, not with the long ones).
-  constexpr int KLPT = KW == 16 ? 8 : 4;
+  // (measured: fewer shuffles pay with the short rows, not with the long ones); with 3-bit keys
+  // every lane takes three words (four 3-byte groups = 32 coordinates) of the row.
+  constexpr int KLPT = K3 ? KW / 3 : (KW == 16 ? 8 : 4);
   constexpr int KTPS = 32 / KLPT;                                           // tokens per warp step (K)
   // V stream: 8 lanes per token (4 tokens per warp step); 4 lanes and 8 tokens with 16-byte rows
   constexpr int VLPT = VW >= 8 ? 8 : 4;
@@ -517,13 +524,34 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   // step): the lane takes words kwl + 4*j of the row, in an order rotated by the
   // token, so that the 32 data-word reads of a step and the 32 table reads of a
   // byte position each fall on 32 different banks.
-  const int kg = KLPT == 4 ? lane >> 2 : tq, kwl = KLPT == 4 ? lane & 3 : wl;
+  const int kg = lane / KLPT, kwl = lane % KLPT;
   int kword[KWPL], vword[VWPL];
   uint32_t ksel[4], kselk[4], kconst[KWPL][4], vconst[VWPL][4];
 #pragma unroll
   for (int m = 0; m < KWPL; ++m) {
-    if (KLPT == 4) kword[m] = KW == 16 ? kwl + 4 * ((m + (kg >> 1)) & 3) : kwl + 4 * ((m + (kg >> 2)) & 1);
+    if (K3) kword[m] = 3 * kwl + m;
+    else if (KLPT == 4) kword[m] = KW == 16 ? kwl + 4 * ((m + (kg >> 1)) & 3) : kwl + 4 * ((m + (kg >> 2)) & 1);
     else kword[m] = KWPL == 1 ? wl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+  }
+  // 3-bit keys.  A row is a string of 6-bit fields (two coordinates each); the table is
+  // T[field value][field column], 64 x 64 floats, kept in FOUR copies whose columns are rotated
+  // by 4*copy positions.  A lane walks its four 3-byte groups in the stored order and the four
+  // fields of a group in an order rotated by k3rf; with the copy chosen by the token the 32
+  // lanes of a warp step read 32 different banks:
+  //   bank = (16*(kwl & 1) + 4*((group + copy) & 3) + ((field + k3rf) & 3)) mod 32,
+  // and (kwl & 1, copy, k3rf) runs over all 32 combinations across the lanes.
+  const int k3copy = kg & 3;
+  const int k3rf = KLPT == 4 ? 2 * (kwl >> 1) + (kg >> 2) : (kg >> 2);
+  uint32_t k3shr[4], k3const[4][4];
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int ff = (b + k3rf) & 3;
+    k3shr[b] = 18 - 6 * ff; // group value in bits 8..31: field ff sits at bit 26 - 6*ff, wanted at bit 8
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int pos = (16 * kwl + 4 * g + ff + 4 * k3copy) & (P / 2 - 1);
+      k3const[g][b] = table_addr | (uint32_t)(k3copy << 14) | (uint32_t)(pos << 2);
+    }
   }
   const int krot = KLPT == 4 ? (KW == 16 ? (kg & 1) + 2 * (kg >> 2) : (kg & 3)) : tq;
   // V stream lane roles: token vg of the warp step, word slot vwl of its row
@@ -598,7 +626,20 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       // thread -> column (consecutive lanes, consecutive banks), a slice of the byte values
       constexpr int HPT = 16 / (CS_CONSUMERS / 64); // high-nibble values per thread
       const int col = tid & 63, bq = tid >> 6;
-      if (col < KC) {
+      if constexpr (K3) {
+        // thread -> field column and the first coordinate's level (bq = 0..7); all four copies
+        if (col < P / 2) {
+          const float q0 = qr[2 * col], q1 = qr[2 * col + 1];
+          const float av = q0 * kcb[bq];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float val = av + q1 * kcb[i];
+#pragma unroll
+            for (int cp = 0; cp < 4; ++cp)
+              table[cp * 4096 + (bq * 8 + i) * 64 + ((col + 4 * cp) & (P / 2 - 1))] = val;
+          }
+        }
+      } else if (col < KC) {
         if (KE == 2) {
           float lo[16];
           const float q0 = qr[2 * col], q1 = qr[2 * col + 1];
@@ -634,8 +675,8 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // also reads the token's K scale (it arrived with the stage) and keeps a running
     // maximum, so no separate scaling pass is needed.
     // which token of the warp's slice this lane owns after the group reduction
-    const int own_step = KLPT == 4 ? (KSTEPS == 4 ? kwl : (kwl >> 1)) : (KSTEPS == 8 ? wl : (wl >> 1));
-    const bool owner = KLPT == 4 ? (KSTEPS == 4 || (kwl & 1) == 0) : (KSTEPS == 8 || (wl & 1) == 0);
+    const int own_step = KLPT == 2 ? kwl : KLPT == 4 ? (KSTEPS == 4 ? kwl : (kwl >> 1)) : (KSTEPS == 8 ? wl : (wl >> 1));
+    const bool owner = KLPT == 2 ? true : KLPT == 4 ? (KSTEPS == 4 || (kwl & 1) == 0) : (KSTEPS == 8 || (wl & 1) == 0);
     const int own_tok = warp * (TKN / CS_WARPS) + KTPS * own_step + kg;
     float lane_max = -1e30f; // where upstream's running maximum starts (attention.cpp:384)
     for (int t = t0; t < t1; t += TKN) {
@@ -655,18 +696,37 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
 #pragma unroll
       for (int s = 0; s < KSTEPS; ++s) {
         float a0 = 0.f, a1 = 0.f;
+        if constexpr (K3) {
+          // the lane's four 3-byte groups, big-endian, in bits 8..31 (the low byte is never used)
+          uint32_t g3[4];
+          g3[0] = __byte_perm(dk[s][0], 0u, 0x0124);
+          g3[1] = __byte_perm(dk[s][0], dk[s][1], 0x3450);
+          g3[2] = __byte_perm(dk[s][1], dk[s][2], 0x2340);
+          g3[3] = __byte_perm(dk[s][2], 0u, 0x1230);
 #pragma unroll
-        for (int m = 0; m < KWPL; ++m) {
-          const uint32_t d = dk[s][m];
-          a0 += lds_f32(__byte_perm(d, kconst[m][0], kselk[0]));
-          a1 += lds_f32(__byte_perm(d, kconst[m][1], kselk[1]));
-          a0 += lds_f32(__byte_perm(d, kconst[m][2], kselk[2]));
-          a1 += lds_f32(__byte_perm(d, kconst[m][3], kselk[3]));
+          for (int g = 0; g < 4; ++g) {
+            a0 += lds_f32(((g3[g] >> k3shr[0]) & 0x3F00u) | k3const[g][0]);
+            a1 += lds_f32(((g3[g] >> k3shr[1]) & 0x3F00u) | k3const[g][1]);
+            a0 += lds_f32(((g3[g] >> k3shr[2]) & 0x3F00u) | k3const[g][2]);
+            a1 += lds_f32(((g3[g] >> k3shr[3]) & 0x3F00u) | k3const[g][3]);
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < KWPL; ++m) {
+            const uint32_t d = dk[s][m];
+            a0 += lds_f32(__byte_perm(d, kconst[m][0], kselk[0]));
+            a1 += lds_f32(__byte_perm(d, kconst[m][1], kselk[1]));
+            a0 += lds_f32(__byte_perm(d, kconst[m][2], kselk[2]));
+            a1 += lds_f32(__byte_perm(d, kconst[m][3], kselk[3]));
+          }
         }
         pv[s] = a0 + a1;
       }
       float total;
-      if constexpr (KLPT == 4) total = quad_transpose_sum<KSTEPS>(pv, kwl);
+      if constexpr (KLPT == 2) { // lane kwl keeps step kwl
+        const float keep = kwl ? pv[1] : pv[0], send = kwl ? pv[0] : pv[1];
+        total = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+      } else if constexpr (KLPT == 4) total = quad_transpose_sum<KSTEPS>(pv, kwl);
       else total = group_transpose_sum<KSTEPS>(pv, wl);
       if (own_valid) {
         const float logit = total * attn_s * ksv;

@@ -84,6 +84,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS, help="sequences per GPU (default: the contract's 256)")
     ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--k-bits", type=int, default=K_BITS, choices=[2, 3, 4], help="decode mode: key width (the contract's is 4)")
+    ap.add_argument("--v-bits", type=int, default=V_BITS, choices=[2, 3, 4],
+                    help="decode mode: value width (the contract's is 2; 3 runs on the general kernel)")
     ap.add_argument("--mode", default="decode", choices=["decode", "append", "latency", "longctx"],
                     help="append: only the bulk-append kernel benchmark; latency: per-token decode latency of the "
                          "small per-layer configurations (contract configurations 1-3); longctx: one 131072-token "
@@ -695,7 +698,8 @@ def run_ours(args):
     alg_bytes = heads * (n * (DIM * K_BITS // 8 + DIM * V_BITS // 8 + 8) + 8 * DIM)
     kt = sum(kern_ms) / len(kern_ms) / 1e3
     clk = clocks["sm_mhz"] / clocks["sm_max_mhz"] if clocks.get("sm_mhz") and clocks.get("sm_max_mhz") else None
-    roof = {"bound": "hbm", "kernel": "compute_stream_kernel<K4,V2,dim128>", "achieved": alg_bytes / kt / 1e9,
+    roof = {"bound": "hbm", "kernel": (f"compute_stream_kernel<K{K_BITS},V{V_BITS},dim128>" if V_BITS != 3 else
+                       f"compute_general_kernel<by words> K{K_BITS}/V{V_BITS} dim128"), "achieved": alg_bytes / kt / 1e9,
             "peak": peak, "unit": "GB/s", "frac": alg_bytes / kt / 1e9 / peak, "peak_source": peak_src,
             # the same fraction had the SM clock stayed at its maximum (kernel time x median MHz / max MHz):
             # separates the share of the power cap from the kernel's own
@@ -759,7 +763,9 @@ def run_ours(args):
 
 
 def main():
+    global K_BITS, V_BITS
     args = parse()
+    K_BITS, V_BITS = args.k_bits, args.v_bits
     claim_stdout()
     if args.impl == "reference":
         run_reference(args)

@@ -446,7 +446,7 @@ bool launch_rows_bits(Group *g, const AppendLaunch &a, int bits) {
   }
 }
 
-// Keys and values together (both quantised): one launch, blockIdx.y = side.
+// Keys and values together (values quantised, keys quantised or FP32): one launch, blockIdx.y = side.
 template <int P, int KB, int VB>
 bool launch_pair(Group *g, const AppendLaunch &ak, const AppendLaunch &av) {
   constexpr size_t SMEM = ((size_t)AT_TILE * (P + 4) + (size_t)(AT_THREADS / 32) * P) * sizeof(float);
@@ -474,6 +474,7 @@ bool launch_pair_kv(Group *g, const AppendLaunch &ak, const AppendLaunch &av, in
   switch (kb) {
   case 2: return launch_pair_v<P, 2>(g, ak, av, vb);
   case 3: return launch_pair_v<P, 3>(g, ak, av, vb);
+  case 16: return launch_pair_v<P, 16>(g, ak, av, vb); // FP32 keys (layer-0 passthrough) beside quantised values
   default: return launch_pair_v<P, 4>(g, ak, av, vb);
   }
 }
@@ -550,7 +551,7 @@ bool append_device(Group *g, const float *dk, const float *dv, int head0, int he
   }
   const int align_k = ((reinterpret_cast<uintptr_t>(dk) & 15) == 0) && (token_stride % 4 == 0);
   const int align_v = ((reinterpret_cast<uintptr_t>(dv) & 15) == 0) && (token_stride % 4 == 0);
-  if (g->c.k_bits != 16 && g->c.v_bits != 16) {
+  if (g->c.v_bits != 16) {
     AppendLaunch ak = a, av = a;
     ak.which = 0; ak.src = dk;
     av.which = 1; av.src = dv;

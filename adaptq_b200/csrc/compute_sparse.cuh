@@ -53,6 +53,31 @@ __device__ __forceinline__ float sp_block_reduce(float v, float *red, bool is_ma
   return r;
 }
 
+// Upstream's sequential walk (attention.cpp:455-473): add arr[0], arr[1], ... while the running
+// mass is below `limit`; returns how many were added.  The sums are strictly sequential (that
+// fixes the cut); the values are fetched eight at a time ahead of the sum so that the chain is
+// one addition and one comparison per element, not a shared-memory round trip.
+__device__ __forceinline__ int walk_mass(const float *arr, int len, float limit, float &mass) {
+  int i = 0, cnt = 0;
+  bool open = true;
+  while (open && i < len) {
+    float x[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x[k] = arr[min(i + k, len - 1)];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (open && i + k < len && mass < limit) {
+        mass = __fadd_rn(mass, x[k]);
+        ++cnt;
+      } else {
+        open = false;
+      }
+    }
+    i += 8;
+  }
+  return cnt;
+}
+
 // V rows of the first `count` sorted tokens, by words (padded dimension a multiple of 32):
 // s_w[i] already holds w * vscale / sqrt(p).  `buf` takes sparse_fold_bytes() for the fold.
 template <int BITS>
@@ -143,9 +168,8 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   if (tid == 0) {
     float mass = 0.f;
     int ii = 0;
-    if (c.sparse_block == 4)
-      for (; ii + 3 < n && mass < c.v_mass; ii += 4) mass = __fadd_rn(mass, bsum[ii >> 2]);
-    for (; ii < n && mass < c.v_mass; ++ii) mass = __fadd_rn(mass, s_w[ii]);
+    if (c.sparse_block == 4) ii = 4 * walk_mass(bsum, n4, c.v_mass, mass);
+    ii += walk_mass(s_w + ii, n - ii, c.v_mass, mass);
     s_count = ii;
   }
   __syncthreads();

@@ -719,7 +719,7 @@ bool launch_stream_t(Group *g, const StreamLaunch &a, int grid) {
 }
 
 bool stream_supported(const CacheView &c) {
-  const bool v_ok = c.v_bits == 4 || c.v_bits == 2;
+  const bool v_ok = c.v_bits == 4 || c.v_bits == 3 || c.v_bits == 2;
   if (c.padded == 128) return (c.k_bits == 4 || c.k_bits == 3 || c.k_bits == 2) && v_ok;
   if (c.padded == 64) return (c.k_bits == 4 || c.k_bits == 3) && v_ok;
   return false;
@@ -727,18 +727,26 @@ bool stream_supported(const CacheView &c) {
 
 // The streaming kernel's instantiation for a handle's shape (stream_supported() holds),
 // one persistent block per SM or per work item, whichever is fewer.
+template <int KB, int KW, int P>
+bool launch_stream_v(Group *g, const StreamLaunch &a, int grid) {
+  switch (a.c.v_bits) {
+  case 2: return launch_stream_t<KB, KW, 2, P / 16>(g, a, grid);
+  case 3: return launch_stream_t<KB, KW, 3, 3 * P / 32>(g, a, grid);
+  default: return launch_stream_t<KB, KW, 4, P / 8>(g, a, grid);
+  }
+}
+
 bool launch_stream_for_shape(Group *g, const StreamLaunch &a) {
   const CacheView &c = a.c;
   const long long items = (long long)a.heads_in_call * a.nq * a.n_splits;
   const int grid = (int)std::min<long long>(items, g->sm_count);
-  const bool v2 = c.v_bits == 2;
   if (c.padded == 128) {
-    if (c.k_bits == 4) return v2 ? launch_stream_t<4, 16, 2, 8>(g, a, grid) : launch_stream_t<4, 16, 4, 16>(g, a, grid);
-    if (c.k_bits == 3) return v2 ? launch_stream_t<3, 12, 2, 8>(g, a, grid) : launch_stream_t<3, 12, 4, 16>(g, a, grid);
-    return v2 ? launch_stream_t<2, 8, 2, 8>(g, a, grid) : launch_stream_t<2, 8, 4, 16>(g, a, grid);
+    if (c.k_bits == 4) return launch_stream_v<4, 16, 128>(g, a, grid);
+    if (c.k_bits == 3) return launch_stream_v<3, 12, 128>(g, a, grid);
+    return launch_stream_v<2, 8, 128>(g, a, grid);
   }
-  if (c.k_bits == 3) return v2 ? launch_stream_t<3, 6, 2, 4>(g, a, grid) : launch_stream_t<3, 6, 4, 8>(g, a, grid);
-  return v2 ? launch_stream_t<4, 8, 2, 4>(g, a, grid) : launch_stream_t<4, 8, 4, 8>(g, a, grid);
+  if (c.k_bits == 3) return launch_stream_v<3, 6, 64>(g, a, grid);
+  return launch_stream_v<4, 8, 64>(g, a, grid);
 }
 
 // Pick the number of KV spans per (head, query): spans are multiples of 64
@@ -1448,7 +1456,7 @@ int adaptq_mha_compute_all_static(adaptq_mha_t h, const float *queries, int quer
     return -1;
   }
   if (!stream_supported(c) || c.v_mass > 0.f || c.hyb > 0) {
-    set_error("adaptq_mha_compute_all_static: needs 2/3/4-bit K and 2/4-bit V at head dim 64/128 (no 2-bit K at 64), dense V, no hybrid window");
+    set_error("adaptq_mha_compute_all_static: needs 2/3/4-bit K and V at head dim 64/128 (no 2-bit K at 64), dense V, no hybrid window");
     return -1;
   }
   if (!g->uniform) {

@@ -358,6 +358,20 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
                           : c.k_bits == 3 ? score_row_words<3>(kr, lut, P) : score_row_words<2>(kr, lut, P);
         sc[i] = sum * attn_s * ksc[s];
       }
+    } else if (k_f32 && !mirror && (dim & 3) == 0) {
+      // FP32 key rows (16-byte aligned): one thread per token, the whole row in flight at once
+      const float4 *q4 = reinterpret_cast<const float4 *>(qr);
+      for (int i = tid; i < cn; i += CG_THREADS) {
+        const float4 *kr = reinterpret_cast<const float4 *>(kbase + (size_t)(t0 + i) * c.k_row);
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll 8
+        for (int j = 0; j < dim / 4; ++j) {
+          const float4 kv = __ldg(kr + j), qv = q4[j];
+          s0 += qv.x * kv.x + qv.y * kv.y;
+          s1 += qv.z * kv.z + qv.w * kv.w;
+        }
+        sc[i] = (s0 + s1) * attn_s;
+      }
     } else {
 #pragma unroll 4
       for (int i = warp; i < cn; i += CG_WARPS) {

@@ -1,6 +1,6 @@
 // Streaming split-KV decode-attention kernel for the bandwidth-bound shapes
-// (2-, 3- or 4-bit K with 2- or 4-bit V at padded dimension 128; 3- or 4-bit K with 2- or
-// 4-bit V at 64; dense V).
+// (2-, 3- or 4-bit K and V at padded dimension 128; 3- or 4-bit K with 2-, 3- or 4-bit V at
+// 64; dense V).
 //
 // Replaces the same upstream code as compute_general.cuh -- the quantised
 // branch of AttentionHead::compute (attention/attention.cpp:526-563, :606-633)
@@ -31,7 +31,8 @@
 //    2 bits) instead of one multiply-add per coordinate.  The buckets are
 //    32-bit fixed point (the span's weights are scaled so that they sum to
 //    2^30): integer shared-memory reductions are native and order-independent,
-//    so the result is deterministic; floating-point ones are not native;
+//    so the result is deterministic; floating-point ones are not native.
+//    3-bit values use the 6-bit fields of the key side: bucket[field value][field column];
 //  * one inverse Walsh-Hadamard transform at the end (or in the merge kernel
 //    when the sequence is split);
 //  * a helper warp works one item ahead and one item behind the consumers: it
@@ -199,14 +200,16 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   static_assert(!K3 || KW == 6 || KW == 12, "3-bit keys: padded dimension 64 or 128");
   constexpr int KROW = KW * 4, VROW = VW * 4;
   // tokens per stage; 3-bit rows (24 or 48 bytes) fill 12 KB of a stage with a power of two of tokens
-  constexpr int TKN = K3 ? 12288 / KROW : CS_STAGE_BYTES / KROW, TVN = CS_STAGE_BYTES / VROW;
+  constexpr bool V3 = VB == 3;
+  static_assert(!V3 || VW == 6 || VW == 12, "3-bit values: padded dimension 64 or 128");
+  constexpr int TKN = K3 ? 12288 / KROW : CS_STAGE_BYTES / KROW, TVN = V3 ? 12288 / VROW : CS_STAGE_BYTES / VROW;
   // Lanes that share a token in the K stream: 4 with 32-byte rows, 8 with 64-byte rows
   // (measured: fewer shuffles pay with the short rows, not with the long ones); with 3-bit keys
   // every lane takes three words (four 3-byte groups = 32 coordinates) of the row.
   constexpr int KLPT = K3 ? KW / 3 : (KW == 16 ? 8 : 4);
   constexpr int KTPS = 32 / KLPT;                                           // tokens per warp step (K)
   // V stream: 8 lanes per token (4 tokens per warp step); 4 lanes and 8 tokens with 16-byte rows
-  constexpr int VLPT = VW >= 8 ? 8 : 4;
+  constexpr int VLPT = V3 ? VW / 3 : (VW >= 8 ? 8 : 4);
   constexpr int VTPS = 32 / VLPT;
   constexpr int KSTEPS = TKN / CS_WARPS / KTPS, VSTEPS = TVN / CS_WARPS / VTPS;
   constexpr int KWPL = KW / KLPT, VWPL = VW / VLPT;                         // words per lane
@@ -217,8 +220,10 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   // 16 byte columns (2-bit V at dim 64): the same 128-byte rows hold TWO copies of the 16 columns
   // side by side -- tokens 0..3 of a warp step add into the first, tokens 4..7 into the second --
   // so the 32 lanes of a reduction still fall on 32 different banks; the fold adds the copies.
-  constexpr bool TWOCOPY = VC == 16;
-  constexpr bool COMPACT = VC == 32 || TWOCOPY;
+  // 3-bit values: buckets by 6-bit field, bucket[copy][field value][field column], four
+  // column-rotated copies of 64 x 64 like the 3-bit key table (64 KB).
+  constexpr bool TWOCOPY = !V3 && VC == 16;
+  constexpr bool COMPACT = !V3 && (VC == 32 || TWOCOPY);
   constexpr int VCOLS = TWOCOPY ? 32 : VC;                                 // bucket columns, copies included
   constexpr int BUCKET_BYTES = COMPACT ? 32768 : CS_TABLE_BYTES;           // [256][32 or 64] 32-bit buckets
 
@@ -555,9 +560,23 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   }
   const int krot = KLPT == 4 ? (KW == 16 ? (kg & 1) + 2 * (kg >> 2) : (kg & 3)) : tq;
   // V stream lane roles: token vg of the warp step, word slot vwl of its row
-  const int vg = VLPT == 4 ? lane >> 2 : tq, vwl = VLPT == 4 ? lane & 3 : wl;
+  const int vg = lane / VLPT, vwl = lane % VLPT;
 #pragma unroll
-  for (int m = 0; m < VWPL; ++m) vword[m] = VWPL == 1 ? vwl : ((wl + 8 * (tq >> 1) + 8 * m) & 15);
+  for (int m = 0; m < VWPL; ++m) vword[m] = V3 ? 3 * vwl + m : (VWPL == 1 ? vwl : ((wl + 8 * (tq >> 1) + 8 * m) & 15));
+  // 3-bit values: the same lane roles and bank argument as for 3-bit keys, on the buckets
+  const int v3copy = vg & 3;
+  const int v3rf = VLPT == 4 ? 2 * (vwl >> 1) + (vg >> 2) : (vg >> 2);
+  uint32_t v3shr[4], v3const[4][4];
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int ff = (b + v3rf) & 3;
+    v3shr[b] = 18 - 6 * ff;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int pos = (16 * vwl + 4 * g + ff + 4 * v3copy) & (P / 2 - 1);
+      v3const[g][b] = bucket_addr | (uint32_t)(v3copy << 14) | (uint32_t)(pos << 2);
+    }
+  }
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int kk = (k + vg) & 3;
@@ -801,10 +820,15 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       const uint32_t *stw = reinterpret_cast<const uint32_t *>(stage_ptr(stage));
       uint32_t dv[VSTEPS][VWPL], wv[VSTEPS];
       const uint4 *wp = reinterpret_cast<const uint4 *>(scu + (t - t0) + warp * TPWV + vg * VSTEPS);
+      if constexpr (VSTEPS == 2) {
+        const uint2 w2 = *reinterpret_cast<const uint2 *>(wp);
+        wv[0] = w2.x; wv[1] = w2.y;
+      } else {
 #pragma unroll
-      for (int s4 = 0; s4 < VSTEPS / 4; ++s4) {
-        const uint4 w4 = wp[s4];
-        wv[4 * s4] = w4.x; wv[4 * s4 + 1] = w4.y; wv[4 * s4 + 2] = w4.z; wv[4 * s4 + 3] = w4.w;
+        for (int s4 = 0; s4 < VSTEPS / 4; ++s4) {
+          const uint4 w4 = wp[s4];
+          wv[4 * s4] = w4.x; wv[4 * s4 + 1] = w4.y; wv[4 * s4 + 2] = w4.z; wv[4 * s4 + 3] = w4.w;
+        }
       }
 #pragma unroll
       for (int s = 0; s < VSTEPS; ++s) {
@@ -815,12 +839,25 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
       peek_next();
 #pragma unroll
       for (int s = 0; s < VSTEPS; ++s) {
+        if constexpr (V3) {
+          uint32_t g3[4];
+          g3[0] = __byte_perm(dv[s][0], 0u, 0x0124);
+          g3[1] = __byte_perm(dv[s][0], dv[s][1], 0x3450);
+          g3[2] = __byte_perm(dv[s][1], dv[s][2], 0x2340);
+          g3[3] = __byte_perm(dv[s][2], 0u, 0x1230);
 #pragma unroll
-        for (int m = 0; m < VWPL; ++m) {
+          for (int g = 0; g < 4; ++g) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t ad = __byte_perm(dv[s][m], vconst[m][k], ksel[k]);
-            red_shared_add(COMPACT ? (ad >> 1) : ad, wv[s]);
+            for (int b = 0; b < 4; ++b) red_shared_add(((g3[g] >> v3shr[b]) & 0x3F00u) | v3const[g][b], wv[s]);
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < VWPL; ++m) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t ad = __byte_perm(dv[s][m], vconst[m][k], ksel[k]);
+              red_shared_add(COMPACT ? (ad >> 1) : ad, wv[s]);
+            }
           }
         }
       }
@@ -832,7 +869,44 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     // A thread owns one byte column and a slice of the 256 byte values, reads each
     // bucket once, clears it for the next item and feeds the VE coordinates packed
     // in that byte.
-    {
+    if constexpr (V3) {
+      // A thread owns one field column (two coordinates) and a slice of the 64 field values,
+      // reads its buckets in all four copies, clears them, and weighs by the two digits.
+      constexpr int FC = P / 2, NPARTS = CS_CONSUMERS / FC, VPP = 64 / NPARTS; // 8 parts x 8 values, or 16 x 4
+      const int col = tid % FC, part = tid / FC;
+      const float *vcb = c_cb[1];
+      float hi_sum = 0.f, lo_acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPP; ++i) {
+        const int v = part * VPP + i;
+        uint32_t bi = 0;
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {
+          const int idx = cp * 4096 + v * 64 + ((col + 4 * cp) & (FC - 1));
+          bi += bucket[idx]; // the copies together hold at most the span's total (2^30)
+          bucket[idx] = 0u;
+        }
+        const float bv = (float)bi;
+        hi_sum += bv; // the first digit, (part * VPP) >> 3, is the same for all of this thread's values
+        lo_acc += bv * vcb[v & 7];
+      }
+      const float hi_acc = hi_sum * vcb[(part * VPP) >> 3];
+      sc[part * P + col * 2] = hi_acc * inv_fx;
+      sc[part * P + col * 2 + 1] = lo_acc * inv_fx;
+      consumer_sync();
+      if (tid < P) {
+        float t = 0.f;
+#pragma unroll
+        for (int g = 0; g < NPARTS; ++g) t += sc[g * P + tid];
+        const int ab = idx & 1;
+        guarded_wait(&aempty[ab], (((uint32_t)idx >> 1) & 1u) ^ 1u);
+        float *dst = accb + ab * ACC_PITCH;
+        dst[tid] = t;
+        if (tid == 0) { dst[P] = mx; dst[P + 1] = ls; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&afull[ab]);
+      }
+    } else {
       constexpr int NPARTS = CS_CONSUMERS / VCOLS, BPP = 256 / NPARTS;
       constexpr int LOGB = BPP == 16 ? 4 : 5; // byte value = (part << LOGB) | i
       static_assert(BPP == 16 || BPP == 32, "16 or 32 byte values per thread");

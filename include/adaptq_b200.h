@@ -117,8 +117,8 @@ int adaptq_mha_merge_from_peers(adaptq_mha_t mha, const float *gather_buf,
  * an allocation or free can cause.  Same result as adaptq_mha_compute_all.
  *
  *  - queries, outs: DEVICE memory, float [n_heads][queries_per_head][dim].
- *  - Shapes of the streaming kernel only: K at 2, 3 or 4 bits and V at 2 or
- *    4 bits with head dim 128 (3- or 4-bit K at dim 64), v_mass <= 0,
+ *  - Shapes of the streaming kernel only: K and V at 2, 3 or 4 bits with
+ *    head dim 128 (3- or 4-bit K at dim 64), v_mass <= 0,
  *    hybrid_thresh == 0, all heads holding the same number of tokens.
  *    Anything else returns -1.
  *  - The split-KV partials live in a 4 MiB array inside the library image

@@ -24,6 +24,11 @@ CASES = [
     (128, 3, 4, 2000, 2300, 0.0, 0, "normal"),                   # ... wrapped ring
     (64, 3, 4, 1100, 1030, 0.0, 0, "student4_outlier"),
     (64, 3, 2, 600, 511, 0.0, 0, "normal"),
+    (128, 3, 3, 4096, 4000, 0.0, 0, "normal"),                   # 3-bit values: buckets by 6-bit field
+    (128, 2, 3, 2000, 2300, 0.0, 0, "normal"),                   # ... wrapped ring
+    (128, 4, 3, 9000, 8700, 0.0, 0, "normal"),                   # ... two spans, merged in the launch
+    (64, 4, 3, 1100, 1030, 0.0, 0, "student4_outlier"),
+    (64, 3, 3, 600, 511, 0.0, 0, "normal"),
     (128, 4, 3, 300, 129, 0.0, 0, "normal"),
     (64, 4, 4, 600, 513, 0.0, 0, "normal"),
     (64, 2, 2, 100, 7, 0.0, 0, "normal"),
@@ -224,7 +229,7 @@ def test_streaming_and_general_kernels_agree(gpu_lib, orc):
             gpu_lib.adaptq_set_kernel_policy(0)
 
 
-@pytest.mark.parametrize("kb,vb", [(4, 2), (2, 2), (4, 4), (3, 2)])
+@pytest.mark.parametrize("kb,vb", [(4, 2), (2, 2), (4, 4), (3, 2), (3, 3)])
 def test_heavy_tailed_long_context(gpu_lib, orc, kb, vb):
     """Student-t(3) keys at 20 000 tokens (the long-context config's distribution):
     logits reach the hundreds, a single token can carry >99 % of the mass, and the

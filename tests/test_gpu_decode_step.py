@@ -33,7 +33,7 @@ def test_decode_step_small_against_oracle(gpu_lib, orc):
     ctx.close()
 
 
-@pytest.mark.parametrize("bits", [(4, 2), (2, 4)])
+@pytest.mark.parametrize("bits", [(4, 2), (2, 4), (3, 4)])
 def test_decode_step_pipelined_equals_two_calls(gpu_lib, orc, bits):
     import torch
     import adaptq_b200

@@ -91,9 +91,9 @@ def test_static_scratch_refusals(gpu_lib):
     assert L.adaptq_mha_compute_all_static(None, C.c_void_p(q.data_ptr()), 1, C.c_void_p(o.data_ptr())) == -1
     assert err() == "adaptq_mha_compute_all_static: null handle"
     assert L.adaptq_mha_compute_all_static(ctx._h, C.c_void_p(q.data_ptr()), 0, C.c_void_p(o.data_ptr())) == -1
-    v3 = MHAContext(2, 128, 4, 3, 64, seed=1, v_mass=0.0, hybrid_thresh=0)   # 3-bit V: not a streaming shape
-    assert L.adaptq_mha_compute_all_static(v3._h, C.c_void_p(q.data_ptr()), 1, C.c_void_p(o.data_ptr())) == -1
-    assert "2/4-bit V" in err()
+    k16 = MHAContext(2, 128, 16, 2, 64, seed=1, v_mass=0.0, hybrid_thresh=0)   # FP32 keys: not a streaming shape
+    assert L.adaptq_mha_compute_all_static(k16._h, C.c_void_p(q.data_ptr()), 1, C.c_void_p(o.data_ptr())) == -1
+    assert "needs 2/3/4-bit K and V" in err()
     # too many (span, head, query) partials for the fixed array: refused, not truncated
     big, _ = _ctx(8, 128, 2, 2, 70000, 5, torch)
     nq = 128

@@ -529,7 +529,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   // step): the lane takes words kwl + 4*j of the row, in an order rotated by the
   // token, so that the 32 data-word reads of a step and the 32 table reads of a
   // byte position each fall on 32 different banks.
-  const int kg = lane / KLPT, kwl = lane % KLPT;
+  const int kg = K3 ? (int)((unsigned)lane / KLPT) : (KLPT == 4 ? lane >> 2 : tq), kwl = K3 ? (int)((unsigned)lane % KLPT) : (KLPT == 4 ? lane & 3 : wl);
   int kword[KWPL], vword[VWPL];
   uint32_t ksel[4], kselk[4], kconst[KWPL][4], vconst[VWPL][4];
 #pragma unroll
@@ -560,7 +560,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   }
   const int krot = KLPT == 4 ? (KW == 16 ? (kg & 1) + 2 * (kg >> 2) : (kg & 3)) : tq;
   // V stream lane roles: token vg of the warp step, word slot vwl of its row
-  const int vg = lane / VLPT, vwl = lane % VLPT;
+  const int vg = V3 ? (int)((unsigned)lane / VLPT) : (VLPT == 4 ? lane >> 2 : tq), vwl = V3 ? (int)((unsigned)lane % VLPT) : (VLPT == 4 ? lane & 3 : wl);
 #pragma unroll
   for (int m = 0; m < VWPL; ++m) vword[m] = V3 ? 3 * vwl + m : (VWPL == 1 ? vwl : ((wl + 8 * (tq >> 1) + 8 * m) & 15));
   // 3-bit values: the same lane roles and bank argument as for 3-bit keys, on the buckets

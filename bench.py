@@ -86,7 +86,7 @@ def parse():
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--k-bits", type=int, default=K_BITS, choices=[2, 3, 4], help="decode mode: key width (the contract's is 4)")
     ap.add_argument("--v-bits", type=int, default=V_BITS, choices=[2, 3, 4],
-                    help="decode mode: value width (the contract's is 2; 3 runs on the general kernel)")
+                    help="decode mode: value width (the contract's is 2)")
     ap.add_argument("--mode", default="decode", choices=["decode", "append", "latency", "longctx"],
                     help="append: only the bulk-append kernel benchmark; latency: per-token decode latency of the "
                          "small per-layer configurations (contract configurations 1-3); longctx: one 131072-token "
@@ -94,6 +94,8 @@ def parse():
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="longctx mode: combine the ranks' partials with an NCCL all-gather, or let the kernels store "
                          "them into every rank's buffer over NVLink (torch symmetric memory)")
+    ap.add_argument("--general-kernel", action="store_true",
+                    help="decode mode: force the general-purpose kernels (for profiling them at a streaming shape)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-append-bench", action="store_true")
     ap.add_argument("--skip-longctx", action="store_true", help="leave the long-context measurement out of the default line")
@@ -591,6 +593,8 @@ def run_ours(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     L = adaptq_b200.load()
+    if args.general_kernel:
+        L.adaptq_set_kernel_policy(1)
     peak, peak_src = measured_peak()
     if args.mode == "append":
         if rank == 0:
@@ -698,8 +702,8 @@ def run_ours(args):
     alg_bytes = heads * (n * (DIM * K_BITS // 8 + DIM * V_BITS // 8 + 8) + 8 * DIM)
     kt = sum(kern_ms) / len(kern_ms) / 1e3
     clk = clocks["sm_mhz"] / clocks["sm_max_mhz"] if clocks.get("sm_mhz") and clocks.get("sm_max_mhz") else None
-    roof = {"bound": "hbm", "kernel": (f"compute_stream_kernel<K{K_BITS},V{V_BITS},dim128>" if V_BITS != 3 else
-                       f"compute_general_kernel<by words> K{K_BITS}/V{V_BITS} dim128"), "achieved": alg_bytes / kt / 1e9,
+    roof = {"bound": "hbm", "kernel": (f"compute_general_kernel<by words> K{K_BITS}/V{V_BITS} dim128" if args.general_kernel else
+                       f"compute_stream_kernel<K{K_BITS},V{V_BITS},dim128>"), "achieved": alg_bytes / kt / 1e9,
             "peak": peak, "unit": "GB/s", "frac": alg_bytes / kt / 1e9 / peak, "peak_source": peak_src,
             # the same fraction had the SM clock stayed at its maximum (kernel time x median MHz / max MHz):
             # separates the share of the power cap from the kernel's own

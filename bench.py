@@ -442,10 +442,10 @@ def longctx_check(torch, dist, world, rank, ctx, keep_k, keep_v, q, o, kb, vb, N
     exact = exact_attention_f64(O, hd, q0)
     try:
         assert_close_conditioned(got, want, exact, "long-context head 0")
-        verdict = "ok"
+        outcome = "ok"
     except AssertionError as ex:
-        verdict = f"FAILED: {ex}"
-    return {"result": verdict, "max_abs_err_vs_oracle": float(np.abs(got - want).max()),
+        outcome = f"FAILED: {ex}"
+    return {"result": outcome, "max_abs_err_vs_oracle": float(np.abs(got - want).max()),
             "oracle_abs_err_vs_float64": float(np.abs(want - exact).max()), "head": 0, "tokens": N}
 
 

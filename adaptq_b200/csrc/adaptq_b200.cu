@@ -652,12 +652,12 @@ bool launch_logits(Group *g, ComputeLaunch &a, float *w, int ws) {
 }
 
 template <int ITEMS>
-bool launch_sparse_fused_t(Group *g, const ComputeLaunch &a, const float *w, int ws) {
+bool launch_sparse_fused_t(Group *g, const ComputeLaunch &a, const float *w, int ws, const float *q) {
   const size_t smem = SparseSmem<ITEMS>::bytes + sparse_fold_bytes(g->c.padded, g->c.v_bits);
   static int configured[MAX_DEVICES] = {};
   auto kern = sparse_fused_kernel<ITEMS>;
   if (!ensure_smem_limit(kern, configured, g->device, smem, "compute (sparse V)")) return false;
-  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, a.rot, g->c, a.head0, a.nq, a.out, g->d_status);
+  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, a.rot, g->c, a.head0, a.nq, a.out, g->d_status, q);
   ++g_launches;
   CUDA_TRY(launch_status(), "compute (sparse V)");
   return true;
@@ -670,12 +670,19 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
   const size_t cells = (size_t)items * ws;
   if (cells > (size_t)0x7fffffff) { set_error("compute: sparse-V workspace too large for one call"); return false; }
   if (a.n <= SP_THREADS * 16) { // one block per (head, query) sorts and accumulates in shared memory
-    if (!ensure_scratch(g, cells * 4 + 256)) return false;
-    float *w = static_cast<float *>(g->d_scratch);
-    if (!launch_logits(g, a, w, ws)) return false;
-    if (a.n <= SP_THREADS * 4) return launch_sparse_fused_t<4>(g, a, w, ws);
-    if (a.n <= SP_THREADS * 8) return launch_sparse_fused_t<8>(g, a, w, ws);
-    return launch_sparse_fused_t<16>(g, a, w, ws);
+    // few items: the block also forms its logits (one launch); many items: the logits come from
+    // the general kernel, which spreads each item's rows over many blocks
+    const bool in_block = sparse_logits_in_block(c.padded) && g_policy.load() != 1 && items <= 2 * g->sm_count;
+    float *w = nullptr;
+    if (!in_block) {
+      if (!ensure_scratch(g, cells * 4 + 256)) return false;
+      w = static_cast<float *>(g->d_scratch);
+      if (!launch_logits(g, a, w, ws)) return false;
+    }
+    const float *q = in_block ? a.q : nullptr;
+    if (a.n <= SP_THREADS * 4) return launch_sparse_fused_t<4>(g, a, w, ws, q);
+    if (a.n <= SP_THREADS * 8) return launch_sparse_fused_t<8>(g, a, w, ws, q);
+    return launch_sparse_fused_t<16>(g, a, w, ws, q);
   }
   size_t temp_bytes = 0;
   cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,

@@ -23,9 +23,16 @@
 namespace aq {
 
 constexpr int SP_THREADS = 512;
+#ifndef AQ_SORT_RADIX
+#define AQ_SORT_RADIX 4
+#endif
+// Weights lie in [0, 1], so as IEEE bit patterns their two top bits are always zero: the sort
+// runs over bits 0..29 only.  Padding sorts as weight 0; the sort is stable and the padding
+// sits behind the n real entries, so it stays behind every real token.
+constexpr int SP_SORT_END_BIT = 30;
 
 template <int ITEMS> struct SparseSmem {
-  using Sort = cub::BlockRadixSort<float, SP_THREADS, ITEMS, int>;
+  using Sort = cub::BlockRadixSort<float, SP_THREADS, ITEMS, int, AQ_SORT_RADIX>;
   static constexpr int CAP = SP_THREADS * ITEMS;
   // sort scratch (later reused for the block sums and the group fold) | weights | tokens | vec[1024] | red[64]
   static constexpr size_t sort_bytes = (sizeof(typename Sort::TempStorage) + 15) / 16 * 16;
@@ -35,6 +42,10 @@ template <int ITEMS> struct SparseSmem {
 
 // Bytes of the by-words fold: one row of P floats per warp, or per token group when a packed
 // row has more than 32 units.
+// The block computes its own logits (no separate logits launch) for packed rows of whole words
+// up to padded dimension 128: the [coordinate][level] table then fits the fold space.
+inline bool sparse_logits_in_block(int P) { return P % 32 == 0 && P <= 128; }
+
 inline size_t sparse_fold_bytes(int P, int v_bits) {
   if (P % 32 != 0) return 0;
   const int units = P / (v_bits == 2 ? 16 : v_bits == 3 ? 32 : 8);
@@ -105,7 +116,7 @@ __device__ __forceinline__ void sparse_v_words(const float *s_w, const int *s_to
 
 template <int ITEMS>
 __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *logits, int w_stride, int n, int rot, CacheView c,
-                                                                  int head0, int nq, float *out, int *status) {
+                                                                  int head0, int nq, float *out, int *status, const float *q) {
   using S = SparseSmem<ITEMS>;
   using Sort = typename S::Sort;
   extern __shared__ __align__(16) unsigned char smem_sp[];
@@ -121,19 +132,63 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   const int item = blockIdx.x;
   const int h = head0 + item / nq;
   const int tid = threadIdx.x;
-  const float *lg = logits + (size_t)item * w_stride;
-
-  // ---- softmax weights, exactly as the unfused path: e = exp(l - max), w = e * (1/sum) ----
   float key[ITEMS];
   int val[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) { // logical order (oldest token first); the rows are read by slot
+    const int i = tid * ITEMS + k;
+    val[k] = i + rot < c.cap ? i + rot : i + rot - c.cap;
+  }
+  if (q != nullptr) {
+    // ---- logits in this block (sparse_logits_in_block() holds): the query rotation of
+    // compute_general_kernel (attention.cpp:537-550), then one thread per K row against the
+    // [coordinate][level] table, which borrows the fold space behind the fixed part
+    float *qr = vec, *lut = reinterpret_cast<float *>(smem_sp + S::bytes);
+    const float *qp = q + (size_t)item * dim;
+    const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
+    for (int i = tid; i < P; i += SP_THREADS) qr[i] = i < dim ? qp[i] : 0.f;
+    __syncthreads();
+    float part = 0.f;
+    for (int i = tid; i < dim; i += SP_THREADS) part += qr[i] * qr[i];
+    const float qn = sqrtf(sp_block_reduce(part, red, false) + 1e-12f);
+    const float qinv = 1.f / qn;
+    for (int i = tid; i < P; i += SP_THREADS) qr[i] = qr[i] * qinv * sign_of(sg, i);
+    __syncthreads();
+    block_butterflies(qr, P);
+    const float back = sqrtf((float)P) * qn, isq = 1.f / sqrtf((float)P);
+    for (int i = tid; i < P; i += SP_THREADS) qr[i] = qr[i] * isq * back;
+    __syncthreads();
+    const int L = 1 << c.k_bits;
+    const float *kcb = c_cb[c.k_bits - 2];
+    for (int i = tid; i < P * L; i += SP_THREADS) lut[i] = qr[i / L] * kcb[i % L];
+    __syncthreads();
+    const float attn_s = 1.f / (sqrtf((float)dim) * (float)P);
+    const uint8_t *kbase = c.k_slab + (size_t)h * c.k_stride;
+    const float *ksc = c.k_scale + (size_t)h * c.s_stride;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const int i = tid * ITEMS + k;
+      key[k] = -INFINITY;
+      if (i < n && AQ_CHECK(status, val[k] >= 0 && val[k] < c.cap, 15)) {
+        const uint8_t *kr = kbase + (size_t)val[k] * c.k_row;
+        const float sum = c.k_bits == 4 ? score_row_words<4>(kr, lut, P)
+                          : c.k_bits == 3 ? score_row_words<3>(kr, lut, P) : score_row_words<2>(kr, lut, P);
+        key[k] = sum * attn_s * ksc[val[k]];
+      }
+    }
+    __syncthreads(); // vec and the table are free again
+  } else {
+    const float *lg = logits + (size_t)item * w_stride;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const int i = tid * ITEMS + k;
+      key[k] = i < n ? lg[i] : -INFINITY;
+    }
+  }
+  // ---- softmax weights, exactly as the unfused path: e = exp(l - max), w = e * (1/sum) ----
   float mx = -1e30f;
 #pragma unroll
-  for (int k = 0; k < ITEMS; ++k) {
-    const int i = tid * ITEMS + k;
-    key[k] = i < n ? lg[i] : -INFINITY;
-    val[k] = i + rot < c.cap ? i + rot : i + rot - c.cap; // logits are in logical order; the V rows are read by slot
-    mx = fmaxf(mx, key[k]);
-  }
+  for (int k = 0; k < ITEMS; ++k) mx = fmaxf(mx, key[k]);
   mx = sp_block_reduce(mx, red, true);
   float s = 0.f;
 #pragma unroll
@@ -147,11 +202,11 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
 #pragma unroll
   for (int k = 0; k < ITEMS; ++k) {
     const int i = tid * ITEMS + k;
-    key[k] = i < n ? key[k] * inv : -1.f; // padding sorts behind every real weight (weights are >= 0)
+    key[k] = i < n ? key[k] * inv : 0.f; // padding: weight 0, behind the real tokens (stable sort)
   }
   // ---- stable descending sort of (weight, token) ------------------------------------------
   __syncthreads();
-  Sort(sort_tmp).SortDescending(key, val);
+  Sort(sort_tmp).SortDescending(key, val, 0, SP_SORT_END_BIT);
   __syncthreads();
 #pragma unroll
   for (int k = 0; k < ITEMS; ++k) {

@@ -104,6 +104,11 @@ struct RingState { int head, size, mirror; };
 struct Group {
   uint32_t magic = MAGIC;
   bool single = false;
+  // The decode-step entry points store the library's launch count here right after they have
+  // launched the append kernel on `stream`.  An attention launch that finds the count unchanged
+  // is the very next launch, so the append kernel is its predecessor in the stream and it may
+  // start beside it (programmatic dependent launch); any other launch in between voids it.
+  unsigned long long append_ticket = ~0ull;
   CacheView c{};
   int device = 0;
   int sm_count = 148;
@@ -418,6 +423,30 @@ bool ensure_smem_limit(K kern, int (&slot)[MAX_DEVICES], int device, size_t byte
   return true;
 }
 
+// Launch an attention kernel.  Directly behind this handle's append kernel (g->after_append)
+// the launch carries the programmatic-stream-serialisation attribute: the kernel may start
+// while the append still runs and waits inside (griddep_wait) before it reads the cache.
+template <typename Kern, typename... Args>
+void launch_attention(Group *g, Kern kern, dim3 grid, int threads, size_t smem, Args... args) {
+  const bool pdl = g->append_ticket == g_launches.load();
+  g->append_ticket = ~0ull;
+  if (!pdl) {
+    kern<<<grid, threads, smem, g->stream>>>(args...);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = g->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, args...); // the caller reads the launch status
+}
+
 // ---------------------------------------------------------------------------
 // append
 // ---------------------------------------------------------------------------
@@ -578,7 +607,7 @@ bool launch_general_variant(Group *g, const ComputeLaunch &a, dim3 grid, size_t 
   static int smem_set[MAX_DEVICES] = {};
   auto kern = compute_general_kernel<KW, VW>;
   if (!ensure_smem_limit(kern, smem_set, g->device, smem, what)) return false;
-  kern<<<grid, CG_THREADS, smem, g->stream>>>(a);
+  launch_attention(g, kern, grid, CG_THREADS, smem, a);
   ++g_launches;
   CUDA_TRY(launch_status(), what);
   return true;
@@ -657,7 +686,7 @@ bool launch_sparse_fused_t(Group *g, const ComputeLaunch &a, const float *w, int
   static int configured[MAX_DEVICES] = {};
   auto kern = sparse_fused_kernel<ITEMS>;
   if (!ensure_smem_limit(kern, configured, g->device, smem, "compute (sparse V)")) return false;
-  kern<<<a.heads_in_call * a.nq, SP_THREADS, smem, g->stream>>>(w, ws, a.n, a.rot, g->c, a.head0, a.nq, a.out, g->d_status, q);
+  launch_attention(g, kern, dim3((unsigned)(a.heads_in_call * a.nq)), SP_THREADS, smem, w, ws, a.n, a.rot, g->c, a.head0, a.nq, a.out, g->d_status, q);
   ++g_launches;
   CUDA_TRY(launch_status(), "compute (sparse V)");
   return true;
@@ -719,7 +748,7 @@ bool launch_stream_t(Group *g, const StreamLaunch &a, int grid) {
   auto kern = compute_stream_kernel<KB, KW, VB, VW>;
   static int configured[MAX_DEVICES] = {};
   if (!ensure_smem_limit(kern, configured, g->device, CS_SMEM_BYTES, "compute")) return false;
-  kern<<<grid, CS_THREADS, CS_SMEM_BYTES, g->stream>>>(a);
+  launch_attention(g, kern, dim3((unsigned)grid), CS_THREADS, CS_SMEM_BYTES, a);
   ++g_launches;
   CUDA_TRY(launch_status(), "compute");
   return true;
@@ -843,6 +872,7 @@ bool compute_device(Group *g, const float *dq, float *dout, int head0, int heads
   if (heads_in_call <= 0 || nq <= 0) return true;
   const size_t out_floats = (size_t)heads_in_call * nq * (partial_out ? partial_floats(c) : (size_t)c.dim);
   if (st.size == 0) {
+    g->append_ticket = ~0ull;
     CUDA_TRY(cudaMemsetAsync(dout, 0, out_floats * 4, g->stream), "compute");
     return true;
   }
@@ -1184,9 +1214,14 @@ int adaptq_mha_decode_step(adaptq_mha_t h, const float *keys, const float *vals,
   std::unique_lock<std::mutex> lk(g->mu);
   const bool pipeline = pinned && g->uniform && c.v_mass <= 0.f && c.n_heads >= 4096;
   if (!pipeline) {
+    const bool on_device = g->uniform && ptr_kind(keys) == PK_DEVICE && ptr_kind(vals) == PK_DEVICE &&
+                           ptr_kind(queries) == PK_DEVICE && ptr_kind(outs) == PK_DEVICE;
     lk.unlock();
     if (adaptq_mha_append_batch(h, keys, vals, 1, token_pos) != 0) return -1;
-    return adaptq_mha_compute_all(h, queries, 1, outs);
+    if (on_device) g->append_ticket = g_launches.load(); // no copy sits between the two kernels
+    const int r = adaptq_mha_compute_all(h, queries, 1, outs);
+    g->append_ticket = ~0ull;
+    return r;
   }
   DeviceGuard dg(g->device);
   const size_t row = (size_t)c.dim, all = (size_t)c.n_heads * row * 4, slot = round_up(all, 256);
@@ -1222,7 +1257,10 @@ int adaptq_mha_decode_step(adaptq_mha_t h, const float *keys, const float *vals,
     STEP_TRY(cudaEventRecord(g->ev[ch], g->copy_in));
     STEP_TRY(cudaStreamWaitEvent(g->stream, g->ev[ch], 0));
     if (!append_device(g, dk + off, dv + off, h0, hc, 1, (size_t)c.n_heads * row, before)) return -1;
-    if (!compute_device(g, dq + off, dout + off, h0, hc, 1, after, false)) return -1;
+    g->append_ticket = g_launches.load();
+    const bool computed = compute_device(g, dq + off, dout + off, h0, hc, 1, after, false);
+    g->append_ticket = ~0ull;
+    if (!computed) return -1;
     STEP_TRY(cudaEventRecord(g->ev[CHUNKS + ch], g->stream));
     STEP_TRY(cudaStreamWaitEvent(g->copy_out, g->ev[CHUNKS + ch], 0));
     STEP_TRY(cudaMemcpyAsync(outs + off, dout + off, bytes, cudaMemcpyDeviceToHost, g->copy_out));

@@ -246,6 +246,7 @@ __device__ __forceinline__ void append_item_general(const AppendLaunch &a, long 
 constexpr int GEN_WARPS = 4;
 
 __global__ void __launch_bounds__(GEN_WARPS * 32) append_general_kernel(const AppendLaunch a) {
+  griddep_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_gen[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float *buf = reinterpret_cast<float *>(smem_gen) + (size_t)warp * a.c.padded;
@@ -608,6 +609,7 @@ __device__ __forceinline__ void append_tile_body(const AppendLaunch &a, const fl
 
 template <int P, int BITS>
 __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kernel(const AppendLaunch a) {
+  griddep_launch_dependents();
   append_tile_body<P, BITS>(a, a.src, a.which, (int)blockIdx.x, (int)gridDim.x);
 }
 
@@ -616,6 +618,7 @@ __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_tile_kern
 // ramp-up and tail costs are paid once.
 template <int P, int KB, int VB>
 __global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM) append_pair_kernel(const AppendLaunch a, const float *src_v) {
+  griddep_launch_dependents();
   // a describes the call and carries the key rows in a.src; the value rows start at src_v
   if constexpr (KB == VB) { // one copy of the code serves both sides
     const int which = (int)blockIdx.y;

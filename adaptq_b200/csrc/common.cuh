@@ -88,6 +88,15 @@ __host__ __device__ inline int row_bytes(int padded, int bits) {
   return bits == 16 ? padded * 4 : (padded * bits + 7) / 8;
 }
 
+// Programmatic dependent launch.  A decode step launches the append kernel and then the
+// attention kernel with the stream-serialisation attribute: the append kernel lets the
+// dependent grid start at once (every one of its blocks calls this on entry, so all of them
+// are resident by then), and the attention kernel runs its set-up (barrier initialisation,
+// query rotation, score table) beside the append and waits here, for the whole append grid
+// and its memory, before it first touches the cache.  Without the attribute both are no-ops.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Index j of a packed row (upstream core/quantizer.cpp:156-194 layouts).
 __device__ __forceinline__ int unpack_at(const uint8_t *row, int j, int bits) {
   if (bits == 4) {

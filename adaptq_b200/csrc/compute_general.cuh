@@ -327,6 +327,7 @@ __global__ void __launch_bounds__(CG_THREADS) compute_general_kernel(const Compu
   const float *vsc = c.v_scale + (size_t)h * c.s_stride;
   const float *mir = mirror ? c.mirror + (size_t)h * c.mirror_stride : nullptr;
 
+  griddep_wait(); // the cache (rows, scales, FP32 window) is read from here on
   int t_begin = min(a.n, split * a.span), t_end = min(a.n, t_begin + a.span);
   if (!AQ_CHECK(a.status, t_end <= c.cap && h >= 0 && h < c.n_heads, 12)) t_begin = t_end = 0; // nothing is read
 

@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
     const float attn_s = 1.f / (sqrtf((float)dim) * (float)P);
     const uint8_t *kbase = c.k_slab + (size_t)h * c.k_stride;
     const float *ksc = c.k_scale + (size_t)h * c.s_stride;
+    griddep_wait(); // the cache is read from here on
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const int i = tid * ITEMS + k;

@@ -324,6 +324,7 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
   // ======================= producer warp ====================================
   if (tid >= CS_CONSUMERS && tid < CS_HELPER_TID) {
     if (tid != CS_CONSUMERS) return;
+    griddep_wait(); // everything the cache holds is read through this thread's copies
     int stage = 0;
     uint32_t phase = 0;
     for (int item = item_begin; item < item_end; ++item) {

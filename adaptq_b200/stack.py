@@ -40,6 +40,7 @@ class LayerStack:
         self._h = C.c_void_p(h)
         self.pos = 0
         self._stream = 0
+        self._step_cache = None  # (k, v, q, out, their data pointers, the converted arguments) of the last step()
 
     def _adopt(self, *tensors):
         if torch is None or not any(_is_cuda_tensor(t) for t in tensors):
@@ -79,6 +80,19 @@ class LayerStack:
 
     def step(self, k, v, q, out=None):
         """append(k, v) then compute(q) for every layer, as one library call."""
+        # A decode loop hands over the same four CUDA tensors (refilled in place) every token:
+        # then the shape checks and pointer conversions of the previous call still hold.
+        c = self._step_cache
+        if (c is not None and c[0] is k and c[1] is v and c[2] is q and c[3] is out and
+                (k.data_ptr(), v.data_ptr(), q.data_ptr(), out.data_ptr()) == c[4]):
+            stream = torch.cuda.current_stream().cuda_stream
+            if stream != self._stream:
+                self._L.adaptq_stack_set_stream(self._h, C.c_void_p(int(stream)))
+                self._stream = int(stream)
+            if self._L.adaptq_stack_decode_step(self._h, *c[5], self.pos) < 0:
+                raise RuntimeError(_lib.last_error())
+            self.pos += 1
+            return out
         self._adopt(k, v, q, out)
         kp, kk, _ = _as_arg(k)
         vp, vk, _ = _as_arg(v)
@@ -91,6 +105,10 @@ class LayerStack:
         if self._L.adaptq_stack_decode_step(self._h, kp, vp, qp, op, self.pos) < 0:
             raise RuntimeError(_lib.last_error())
         self.pos += 1
+        if all(_is_cuda_tensor(t) for t in (k, v, q, out)) and kk is k and vk is v and qk is q and ok is out:
+            self._step_cache = (k, v, q, out, (k.data_ptr(), v.data_ptr(), q.data_ptr(), out.data_ptr()), (kp, vp, qp, op))
+        else:
+            self._step_cache = None
         return ok
 
     def reset(self):

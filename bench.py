@@ -380,7 +380,7 @@ def latency_bench(torch):
             for _ in range(5):
                 step()
             torch.cuda.synchronize()
-            steps = 50
+            steps = 200
             t0 = time.perf_counter()
             for _ in range(steps):
                 step()
@@ -395,7 +395,12 @@ def latency_bench(torch):
         launches0 = adaptq_b200.load().adaptq_kernel_launches()
         dt = time_it(lambda: stack.step(kn, kn, q, out=o))
         res.update({"us_per_token": dt * 1e6, "us_per_layer": dt * 1e6 / layers, "tokens_per_s": 1.0 / dt,
-                    "launches_per_token": (adaptq_b200.load().adaptq_kernel_launches() - launches0) / 55, "parts": stack.parts})
+                    "launches_per_token": (adaptq_b200.load().adaptq_kernel_launches() - launches0) / 205, "parts": stack.parts})
+        # the same step through the C ABI alone (adaptq_stack_decode_step with ready-made pointers)
+        import ctypes as C
+        Lc = adaptq_b200.load()
+        cargs = [C.c_void_p(kn.data_ptr()), C.c_void_p(kn.data_ptr()), C.c_void_p(q.data_ptr()), C.c_void_p(o.data_ptr())]
+        res["us_per_token_c_abi"] = time_it(lambda: Lc.adaptq_stack_decode_step(stack._h, *cargs, 0)) * 1e6
         stack.close()
         # (b) upstream's shape: one engine per layer, one decode-step call per layer
         if layers > 1:

@@ -108,7 +108,7 @@ struct Group {
   // launched the append kernel on `stream`.  An attention launch that finds the count unchanged
   // is the very next launch, so the append kernel is its predecessor in the stream and it may
   // start beside it (programmatic dependent launch); any other launch in between voids it.
-  unsigned long long append_ticket = ~0ull;
+  std::atomic<unsigned long long> append_ticket{~0ull};
   CacheView c{};
   int device = 0;
   int sm_count = 148;
@@ -428,8 +428,7 @@ bool ensure_smem_limit(K kern, int (&slot)[MAX_DEVICES], int device, size_t byte
 // while the append still runs and waits inside (griddep_wait) before it reads the cache.
 template <typename Kern, typename... Args>
 void launch_attention(Group *g, Kern kern, dim3 grid, int threads, size_t smem, Args... args) {
-  const bool pdl = g->append_ticket == g_launches.load();
-  g->append_ticket = ~0ull;
+  const bool pdl = g->append_ticket.exchange(~0ull) == g_launches.load();
   if (!pdl) {
     kern<<<grid, threads, smem, g->stream>>>(args...);
     return;

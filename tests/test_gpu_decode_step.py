@@ -33,6 +33,48 @@ def test_decode_step_small_against_oracle(gpu_lib, orc):
     ctx.close()
 
 
+@pytest.mark.parametrize("dim,kb,vb,vm,heads,cap", [
+    (128, 4, 2, 0.0, 5, 700),      # streaming kernel, one span
+    (128, 3, 3, 0.0, 3, 9000),     # streaming kernel, two spans merged in the launch
+    (64, 2, 2, 0.0, 4, 300),       # general kernel
+    (64, 16, 2, 0.0, 4, 300),      # FP32 keys: two append launches in front of the attention kernel
+    (64, 4, 2, 0.95, 4, 500),      # sparse V: logits formed in the sorting block
+])
+def test_device_decode_steps_see_the_token_just_appended(gpu_lib, orc, dim, kb, vb, vm, heads, cap):
+    """Decode steps on device tensors: the attention kernel is launched so that it may start
+    while the append kernel of the same step still runs (it waits inside before reading the
+    cache).  Every step's output must contain the token appended in that step -- checked
+    against the CPU oracle over steps that fill the ring's tail and then evict every time,
+    with a query that points at the new key so that the new token carries most of the weight."""
+    import torch
+    import adaptq_b200
+    from helpers import assert_sparse_close
+    rng = np.random.default_rng(cap + kb)
+    steps = 24
+    k, v = make_kv(rng, cap - steps // 2 + steps, heads, dim)
+    pre = cap - steps // 2
+    ctx = adaptq_b200.MHAContext(heads, dim, kb, vb, cap, seed=11, v_mass=vm, hybrid_thresh=0)
+    cpu = CpuHeads(orc, heads, dim, kb, vb, cap, 11, vm, 0)
+    ctx.append_all(torch.from_numpy(k[:pre]).cuda(), torch.from_numpy(v[:pre]).cuda())
+    cpu.append_many(k[:pre], v[:pre])
+    dk, dv, dq = (torch.empty((heads, dim), device="cuda") for _ in range(3))
+    do = torch.empty((heads, dim), device="cuda")
+    for s in range(steps):
+        t = pre + s
+        q = (k[t] * 0.5 + 0.1 * rng.standard_normal((heads, dim))).astype(np.float32)
+        dk.copy_(torch.from_numpy(k[t])); dv.copy_(torch.from_numpy(v[t])); dq.copy_(torch.from_numpy(q))
+        ctx.decode_step(dk, dv, dq, out=do, pos=t)
+        cpu.append_many(k[t:t + 1], v[t:t + 1])
+        got = do.cpu().numpy()
+        if vm > 0:
+            for h in range(heads):
+                assert_sparse_close(got[h], cpu.heads[h], q[h], vm, f"step {s} head {h}")
+        else:
+            assert_close(got, cpu.compute(q), f"step {s}")
+    ctx.synchronize()
+    ctx.close()
+
+
 @pytest.mark.parametrize("bits", [(4, 2), (2, 4), (3, 4)])
 def test_decode_step_pipelined_equals_two_calls(gpu_lib, orc, bits):
     import torch

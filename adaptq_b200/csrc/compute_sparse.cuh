@@ -89,11 +89,13 @@ __device__ __forceinline__ int walk_mass(const float *arr, int len, float limit,
   return cnt;
 }
 
-// V rows of the first `count` sorted tokens, by words (padded dimension a multiple of 32):
-// s_w[i] already holds w * vscale / sqrt(p).  `buf` takes sparse_fold_bytes() for the fold.
+// V rows of the first `count` sorted tokens, by words (padded dimension a multiple of 32).
+// A token's factor is w * vscale * (1/sqrt p); its V scale is fetched together with its row.
+// `buf` takes sparse_fold_bytes() for the fold.
 template <int BITS>
-__device__ __forceinline__ void sparse_v_words(const float *s_w, const int *s_tok, int count, const uint8_t *vbase, const CacheView &c,
-                                               const float *s_cb, float *buf, float *vec, int *status) {
+__device__ __forceinline__ void sparse_v_words(const float *s_w, const int *s_tok, int count, const uint8_t *vbase, const float *vsc,
+                                               float isp, const CacheView &c, const float *s_cb, float *buf, float *vec,
+                                               int *status) {
   using UU = VUnit<BITS>;
   const int tid = threadIdx.x, P = c.padded;
   const int U = P / UU::NCO, u = tid % U, tg = tid / U, TG = SP_THREADS / U;
@@ -107,11 +109,48 @@ __device__ __forceinline__ void sparse_v_words(const float *s_w, const int *s_to
     if (!AQ_CHECK(status, tok >= 0 && tok < c.cap, 15)) continue;
     uint32_t w[UU::WORDS];
     load_words_be<UU::WORDS>(vunit + (size_t)tok * c.v_row, w);
-    const float wt = s_w[i];
+    const float wt = s_w[i] * __ldg(vsc + tok) * isp;
 #pragma unroll
     for (int k = 0; k < UU::NCO; ++k) acc[k] += wt * s_cb[level_of<BITS, UU::WORDS>(w, k)];
   }
   v_fold_words<BITS, SP_THREADS>(acc, P, buf, vec);
+}
+
+// Inverse transform of vec[32*EPL] and the store of the output, by one warp in registers
+// (core/fwht.cpp:106-134: butterflies, * 1/sqrt p, * sign).
+template <int EPL>
+__device__ __forceinline__ void sparse_finish_warp(const float *vec, float isp, const uint32_t *sg, float *o, int dim, int lane) {
+  float v[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) v[e] = vec[EPL * lane + e];
+  warp_butterflies<EPL>(v, lane);
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const int j = EPL * lane + e;
+    if (j < dim) o[j] = v[e] * isp * sign_of(sg, j);
+  }
+}
+
+// Query rotation (attention.cpp:537-550) by one warp in registers: qr[32*EPL] in shared memory.
+template <int EPL>
+__device__ __forceinline__ void sparse_rotate_warp(const float *qp, const uint32_t *sg, int dim, float *qr, int lane) {
+  constexpr int P = 32 * EPL;
+  float v[EPL];
+  float part = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const int j = EPL * lane + e;
+    v[e] = j < dim ? __ldg(qp + j) : 0.f;
+    part += v[e] * v[e];
+  }
+  const float qn = sqrtf(warp_sum(part) + 1e-12f);
+  const float qinv = 1.f / qn;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) v[e] = v[e] * qinv * sign_of(sg, EPL * lane + e);
+  warp_butterflies<EPL>(v, lane);
+  const float back = sqrtf((float)P) * qn, isq = 1.f / sqrtf((float)P);
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) qr[EPL * lane + e] = v[e] * isq * back;
 }
 
 template <int ITEMS>
@@ -146,17 +185,11 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
     float *qr = vec, *lut = reinterpret_cast<float *>(smem_sp + S::bytes);
     const float *qp = q + (size_t)item * dim;
     const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
-    for (int i = tid; i < P; i += SP_THREADS) qr[i] = i < dim ? qp[i] : 0.f;
-    __syncthreads();
-    float part = 0.f;
-    for (int i = tid; i < dim; i += SP_THREADS) part += qr[i] * qr[i];
-    const float qn = sqrtf(sp_block_reduce(part, red, false) + 1e-12f);
-    const float qinv = 1.f / qn;
-    for (int i = tid; i < P; i += SP_THREADS) qr[i] = qr[i] * qinv * sign_of(sg, i);
-    __syncthreads();
-    block_butterflies(qr, P);
-    const float back = sqrtf((float)P) * qn, isq = 1.f / sqrtf((float)P);
-    for (int i = tid; i < P; i += SP_THREADS) qr[i] = qr[i] * isq * back;
+    if (tid < 32) { // sparse_logits_in_block(): the padded dimension is 32, 64 or 128
+      if (P == 128) sparse_rotate_warp<4>(qp, sg, dim, qr, tid);
+      else if (P == 64) sparse_rotate_warp<2>(qp, sg, dim, qr, tid);
+      else sparse_rotate_warp<1>(qp, sg, dim, qr, tid);
+    }
     __syncthreads();
     const int L = 1 << c.k_bits;
     const float *kcb = c_cb[c.k_bits - 2];
@@ -220,6 +253,7 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   const int n4 = n / 4;
   for (int b = tid; b < n4; b += SP_THREADS)
     bsum[b] = __fadd_rn(__fadd_rn(__fadd_rn(s_w[4 * b], s_w[4 * b + 1]), s_w[4 * b + 2]), s_w[4 * b + 3]);
+  if (tid < 16) red[32 + tid] = tid < (1 << c.v_bits) ? c_cb[c.v_bits - 2][tid] : 0.f; // V centroids for the by-words path
   __syncthreads();
   if (tid == 0) {
     float mass = 0.f;
@@ -235,20 +269,20 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   const float *vsc = c.v_scale + (size_t)h * c.s_stride;
   const float *vcb = c_cb[c.v_bits - 2];
   const float isp = 1.f / sqrtf((float)P);
-  for (int i = tid; i < count; i += SP_THREADS)
-    if (AQ_CHECK(status, s_tok[i] >= 0 && s_tok[i] < c.cap, 15)) s_w[i] = s_w[i] * vsc[s_tok[i]] * isp;
-  __syncthreads();
   // ---- V rows of the chosen tokens -------------------------------------------------------------
   if (P % 32 == 0) {
-    // by words: thread = (unit of a row, token group); the units of a row are read side by side
+    // by words: thread = (unit of a row, token group); the units of a row are read side by side.
+    // (the centroid copy in red[32..47] was written before the walk's barrier)
     float *s_cb = red + 32;
-    if (tid < 16) s_cb[tid] = tid < (1 << c.v_bits) ? vcb[tid] : 0.f;
-    __syncthreads();
     float *fold = reinterpret_cast<float *>(smem_sp + S::bytes); // sparse_fold_bytes() behind the fixed part
-    if (c.v_bits == 2) sparse_v_words<2>(s_w, s_tok, count, vbase, c, s_cb, fold, vec, status);
-    else if (c.v_bits == 3) sparse_v_words<3>(s_w, s_tok, count, vbase, c, s_cb, fold, vec, status);
-    else sparse_v_words<4>(s_w, s_tok, count, vbase, c, s_cb, fold, vec, status);
+    if (c.v_bits == 2) sparse_v_words<2>(s_w, s_tok, count, vbase, vsc, isp, c, s_cb, fold, vec, status);
+    else if (c.v_bits == 3) sparse_v_words<3>(s_w, s_tok, count, vbase, vsc, isp, c, s_cb, fold, vec, status);
+    else sparse_v_words<4>(s_w, s_tok, count, vbase, vsc, isp, c, s_cb, fold, vec, status);
   } else {
+    // per-token factor w * vscale * (1/sqrt p), in place
+    for (int i = tid; i < count; i += SP_THREADS)
+      if (AQ_CHECK(status, s_tok[i] >= 0 && s_tok[i] < c.cap, 15)) s_w[i] = s_w[i] * vsc[s_tok[i]] * isp;
+    __syncthreads();
     // by bytes: thread = (column, token group)
     const int TG = P < SP_THREADS ? SP_THREADS / P : 1;
     const int jcol = P < SP_THREADS ? tid % P : tid;
@@ -271,9 +305,17 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
     }
   }
   __syncthreads();
-  block_butterflies(vec, P);
   const uint32_t *sg = c.signs + (size_t)h * c.sign_words;
   float *o = out + (size_t)item * dim;
+  if (P == 32 || P == 64 || P == 128) { // one warp, in registers: no block barriers
+    if (tid < 32) {
+      if (P == 128) sparse_finish_warp<4>(vec, isp, sg, o, dim, tid);
+      else if (P == 64) sparse_finish_warp<2>(vec, isp, sg, o, dim, tid);
+      else sparse_finish_warp<1>(vec, isp, sg, o, dim, tid);
+    }
+    return;
+  }
+  block_butterflies(vec, P);
   for (int j = tid; j < dim; j += SP_THREADS) o[j] = vec[j] * isp * sign_of(sg, j);
 }
 

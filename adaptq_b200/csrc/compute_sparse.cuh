@@ -10,7 +10,8 @@
 // first like upstream's slot list (attention.cpp:562-563), so equal weights keep
 // that order through the stable sort -- the order a stable sort of upstream's
 // list would give (upstream's std::sort leaves ties unspecified).  Here: softmax in
-// registers, a stable block-wide radix sort of (weight, token) pairs, the
+// registers, a stable block-wide radix sort of (weight, token) pairs (written here:
+// block_sort_pairs), the
 // block sums ((w0+w1)+w2)+w3 in parallel and the running mass sequentially in
 // upstream's association (so the cut is the one a sequential walk finds), then
 // the V rows of the chosen tokens with token groups in parallel, one inverse
@@ -18,30 +19,107 @@
 #pragma once
 #include "common.cuh"
 #include "compute_general.cuh"
-#include <cub/block/block_radix_sort.cuh>
 
 namespace aq {
 
 constexpr int SP_THREADS = 512;
-#ifndef AQ_SORT_RADIX
-#define AQ_SORT_RADIX 4
-#endif
-// Weights lie in [0, 1], so as IEEE bit patterns their two top bits are always zero: the sort
-// runs over bits 0..29 only.  Padding sorts as weight 0; the sort is stable and the padding
-// sits behind the n real entries, so it stays behind every real token.
-constexpr int SP_SORT_END_BIT = 30;
+constexpr int SP_WARPS = SP_THREADS / 32;
+// Sort counters: 256 digit values x 16 warps, one padding word per digit so that the 32 lanes
+// of a warp, which update different digits of their own warp's column, fall on different banks.
+constexpr int SP_CNT_PITCH = SP_WARPS + 1;
+constexpr int SP_CNT_WORDS = 256 * SP_CNT_PITCH;                      // 4352
+constexpr int SP_CNT_PER_THREAD = (SP_CNT_WORDS + SP_THREADS - 1) / SP_THREADS; // 9
 
 template <int ITEMS> struct SparseSmem {
-  using Sort = cub::BlockRadixSort<float, SP_THREADS, ITEMS, int, AQ_SORT_RADIX>;
   static constexpr int CAP = SP_THREADS * ITEMS;
-  // sort scratch (later reused for the block sums and the group fold) | weights | tokens | vec[1024] | red[64]
-  static constexpr size_t sort_bytes = (sizeof(typename Sort::TempStorage) + 15) / 16 * 16;
+  // scratch (sort counters, later the block sums and the byte-path fold) | weights | tokens | vec[1024] | red[64]
+  static constexpr size_t sort_bytes = (size_t)SP_CNT_PER_THREAD * SP_THREADS * 4;
   static constexpr size_t scratch_bytes = sort_bytes > (size_t)CAP ? sort_bytes : (size_t)CAP; // >= CAP/4 floats and >= SP_THREADS floats
   static constexpr size_t bytes = scratch_bytes + (size_t)CAP * 8 + 1024 * 4 + 64 * 4; // a multiple of 16
 };
 
-// Bytes of the by-words fold: one row of P floats per warp, or per token group when a packed
-// row has more than 32 units.
+// Position of item k of thread tid: a warp holds 32*ITEMS consecutive positions, item k of its
+// lanes 32 consecutive ones.  (The sort ranks a warp's items k = 0, 1, ... in turn.)
+template <int ITEMS> __device__ __forceinline__ int sp_pos(int tid, int k) { return (tid >> 5) * (32 * ITEMS) + k * 32 + (tid & 31); }
+
+// Stable block-wide sort of (weight, token) pairs, largest weight first, equal weights in the
+// order of their positions; the result goes to s_w[0..CAP) / s_tok[0..CAP).
+// Weights lie in [0, 1], so their IEEE bit patterns occupy 30 bits and order like integers; the
+// sort runs on the complemented pattern (ascending) with four least-significant-digit passes of
+// 8 bits.  A pass: every warp counts its digits (lanes with equal digits find each other with
+// match.any; the items of a warp are ranked k = 0, 1, ... in turn so that a running per-warp
+// count gives the rank among the warp's earlier items), the counts [digit][warp] are scanned in
+// that order over the block, and the pairs move to their ranks through s_w / s_tok.
+// Padding (weight 0 at positions >= n) ties with real zero weights and stays behind them.
+template <int ITEMS>
+__device__ __forceinline__ void block_sort_pairs(float (&key)[ITEMS], int (&val)[ITEMS], float *s_w, int *s_tok, uint32_t *cnt,
+                                                 uint32_t *warp_tot) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t *s_u = reinterpret_cast<uint32_t *>(s_w);
+  uint32_t u[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) u[k] = ~__float_as_uint(key[k]) & 0x3FFFFFFFu;
+  const uint32_t lt = (1u << lane) - 1u;
+#pragma unroll 1
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 8 * pass;
+    for (int e = tid; e < SP_CNT_PER_THREAD * SP_THREADS; e += SP_THREADS) cnt[e] = 0u;
+    __syncthreads();
+    uint32_t rank[ITEMS];
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t d = (u[k] >> shift) & 255u;
+      const uint32_t same = __match_any_sync(0xffffffffu, d);
+      uint32_t *slot = cnt + d * SP_CNT_PITCH + warp;
+      const uint32_t before = *slot;
+      __syncwarp();
+      if (lane == __ffs(same) - 1) *slot = before + __popc(same);
+      __syncwarp();
+      rank[k] = before + __popc(same & lt);
+    }
+    __syncthreads();
+    // exclusive scan of the counts in the order [digit][warp]
+    {
+      uint32_t loc[SP_CNT_PER_THREAD], tsum = 0u;
+      const int e0 = tid * SP_CNT_PER_THREAD;
+#pragma unroll
+      for (int j = 0; j < SP_CNT_PER_THREAD; ++j) { loc[j] = cnt[e0 + j]; tsum += loc[j]; }
+      uint32_t inc = tsum;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += t;
+      }
+      if (lane == 31) warp_tot[warp] = inc;
+      __syncthreads();
+      uint32_t base = inc - tsum;
+      for (int w = 0; w < warp; ++w) base += warp_tot[w];
+#pragma unroll
+      for (int j = 0; j < SP_CNT_PER_THREAD; ++j) { cnt[e0 + j] = base; base += loc[j]; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t d = (u[k] >> shift) & 255u;
+      const uint32_t r = cnt[d * SP_CNT_PITCH + warp] + rank[k];
+      s_u[r] = u[k];
+      s_tok[r] = val[k];
+    }
+    __syncthreads();
+    if (pass < 3) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const int p = sp_pos<ITEMS>(tid, k);
+        u[k] = s_u[p];
+        val[k] = s_tok[p];
+      }
+    }
+  }
+  // complemented patterns back to weights, in place
+  for (int p = tid; p < SP_THREADS * ITEMS; p += SP_THREADS) s_u[p] = ~s_u[p] & 0x3FFFFFFFu;
+  __syncthreads();
+}
+
 // The block computes its own logits (no separate logits launch) for packed rows of whole words
 // up to padded dimension 128: the [coordinate][level] table then fits the fold space.
 inline bool sparse_logits_in_block(int P) { return P % 32 == 0 && P <= 128; }
@@ -157,9 +235,7 @@ template <int ITEMS>
 __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *logits, int w_stride, int n, int rot, CacheView c,
                                                                   int head0, int nq, float *out, int *status, const float *q) {
   using S = SparseSmem<ITEMS>;
-  using Sort = typename S::Sort;
   extern __shared__ __align__(16) unsigned char smem_sp[];
-  typename Sort::TempStorage &sort_tmp = *reinterpret_cast<typename Sort::TempStorage *>(smem_sp);
   float *scratch = reinterpret_cast<float *>(smem_sp);
   float *s_w = reinterpret_cast<float *>(smem_sp + S::scratch_bytes);
   int *s_tok = reinterpret_cast<int *>(s_w + S::CAP);
@@ -175,7 +251,7 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   int val[ITEMS];
 #pragma unroll
   for (int k = 0; k < ITEMS; ++k) { // logical order (oldest token first); the rows are read by slot
-    const int i = tid * ITEMS + k;
+    const int i = sp_pos<ITEMS>(tid, k);
     val[k] = i + rot < c.cap ? i + rot : i + rot - c.cap;
   }
   if (q != nullptr) {
@@ -201,7 +277,7 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
     griddep_wait(); // the cache is read from here on
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
-      const int i = tid * ITEMS + k;
+      const int i = sp_pos<ITEMS>(tid, k);
       key[k] = -INFINITY;
       if (i < n && AQ_CHECK(status, val[k] >= 0 && val[k] < c.cap, 15)) {
         const uint8_t *kr = kbase + (size_t)val[k] * c.k_row;
@@ -215,7 +291,7 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
     const float *lg = logits + (size_t)item * w_stride;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
-      const int i = tid * ITEMS + k;
+      const int i = sp_pos<ITEMS>(tid, k);
       key[k] = i < n ? lg[i] : -INFINITY;
     }
   }
@@ -227,7 +303,7 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   float s = 0.f;
 #pragma unroll
   for (int k = 0; k < ITEMS; ++k) {
-    const int i = tid * ITEMS + k;
+    const int i = sp_pos<ITEMS>(tid, k);
     key[k] = i < n ? expf(key[k] - mx) : 0.f;
     s += key[k];
   }
@@ -235,19 +311,12 @@ __global__ void __launch_bounds__(SP_THREADS) sparse_fused_kernel(const float *l
   const float inv = 1.f / s;
 #pragma unroll
   for (int k = 0; k < ITEMS; ++k) {
-    const int i = tid * ITEMS + k;
+    const int i = sp_pos<ITEMS>(tid, k);
     key[k] = i < n ? key[k] * inv : 0.f; // padding: weight 0, behind the real tokens (stable sort)
   }
-  // ---- stable descending sort of (weight, token) ------------------------------------------
+  // ---- stable descending sort of (weight, token) into s_w / s_tok ---------------------------
   __syncthreads();
-  Sort(sort_tmp).SortDescending(key, val, 0, SP_SORT_END_BIT);
-  __syncthreads();
-#pragma unroll
-  for (int k = 0; k < ITEMS; ++k) {
-    s_w[tid * ITEMS + k] = key[k];
-    s_tok[tid * ITEMS + k] = val[k];
-  }
-  __syncthreads();
+  block_sort_pairs<ITEMS>(key, val, s_w, s_tok, reinterpret_cast<uint32_t *>(scratch), reinterpret_cast<uint32_t *>(red) + 48);
   // ---- the cut: blocks of four while four remain and the mass is short, then singles -------
   float *bsum = scratch; // the sort scratch is free now
   const int n4 = n / 4;

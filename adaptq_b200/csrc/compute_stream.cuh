@@ -643,9 +643,12 @@ __global__ void __launch_bounds__(CS_THREADS, 1) compute_stream_kernel(const Str
     const float *qr = qrot + qb * 128;
     // ---- build the K byte table ----------------------------------------------------
     {
-      // thread -> column (consecutive lanes, consecutive banks), a slice of the byte values
-      constexpr int HPT = 16 / (CS_CONSUMERS / 64); // high-nibble values per thread
-      const int col = tid & 63, bq = tid >> 6;
+      // thread -> column (consecutive lanes, consecutive banks), a slice of the byte values;
+      // with 32 byte columns (2-bit keys at dim 128, 4-bit at dim 64) the threads split the byte
+      // values 16 ways instead of 8 so that none is idle
+      constexpr int TCOLS = (!K3 && KC == 32) ? 32 : 64;
+      constexpr int HPT = 16 / (CS_CONSUMERS / TCOLS); // high-nibble values per thread
+      const int col = tid & (TCOLS - 1), bq = TCOLS == 32 ? tid >> 5 : tid >> 6;
       if constexpr (K3) {
         // thread -> field column and the first coordinate's level (bq = 0..7); all four copies
         if (col < P / 2) {

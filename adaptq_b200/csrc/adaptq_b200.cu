@@ -1242,13 +1242,40 @@ int adaptq_mha_decode_step(adaptq_mha_t h, const float *keys, const float *vals,
   STEP_TRY(cudaStreamWaitEvent(g->copy_in, g->ev[2 * CHUNKS], 0));
   const RingState before = g->u, after = advance(c, before, 1);
   // about an eighth of the heads per chunk, rounded down to whole waves of persistent
-  // blocks (one head per SM per round) so that no chunk ends on a partly filled wave
-  int per = (c.n_heads + 7) / 8;
-  if (per >= g->sm_count) per -= per % g->sm_count;
-  per = std::max(per, (c.n_heads + CHUNKS - 1) / CHUNKS);
-  for (int ch = 0; ch < CHUNKS; ++ch) {
-    const int h0 = ch * per, hc = std::min(per, c.n_heads - h0);
-    if (hc <= 0) break;
+  // blocks (one head per SM per round) so that no chunk ends on a partly filled wave; with
+  // enough heads the first and the last chunk are small (a 32nd), because the upload of the
+  // first and the download of the last are the transfers that nothing hides
+  int cut[CHUNKS + 1];
+  int n_chunks = 0;
+  {
+    const int nh = c.n_heads, sm = g->sm_count;
+    int small = nh / 32;
+    small -= small % sm;
+    cut[0] = 0;
+    if (small >= sm) {
+      int per = (nh - 2 * small + 7) / 8;
+      if (per >= sm) per -= per % sm;
+      per = std::max(per, (nh - 2 * small + CHUNKS - 3) / (CHUNKS - 2));
+      int pos = small;
+      cut[++n_chunks] = pos;
+      while (pos < nh - small && n_chunks < CHUNKS - 1) {
+        pos = std::min(pos + per, nh - small);
+        cut[++n_chunks] = pos;
+      }
+      cut[++n_chunks] = nh;
+    } else {
+      int per = (nh + 7) / 8;
+      if (per >= sm) per -= per % sm;
+      per = std::max(per, (nh + CHUNKS - 1) / CHUNKS);
+      for (int pos = 0; pos < nh;) {
+        pos = std::min(pos + per, nh);
+        cut[++n_chunks] = pos;
+      }
+    }
+  }
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int h0 = cut[ch], hc = cut[ch + 1] - cut[ch];
+    if (hc <= 0) continue;
     const size_t off = (size_t)h0 * row, bytes = (size_t)hc * row * 4;
     STEP_TRY(cudaMemcpyAsync(dk + off, keys + off, bytes, cudaMemcpyHostToDevice, g->copy_in));
     STEP_TRY(cudaMemcpyAsync(dv + off, vals + off, bytes, cudaMemcpyHostToDevice, g->copy_in));

@@ -80,7 +80,7 @@ def test_decode_step_pipelined_equals_two_calls(gpu_lib, orc, bits):
     import torch
     import adaptq_b200
     from oracle import loader
-    heads, dim, cap = 4096 + 40, 128, 96  # not a multiple of the chunk count
+    heads, dim, cap = 6000 + 40, 128, 96  # not a multiple of the chunk count; enough for the small first and last chunk
     kb, vb = bits
     sample = (0, 517, heads - 1)          # these heads are also run on the CPU oracle
     cpu = {h: loader.Head(orc, dim, kb, vb, cap, loader.mha_head_seed(5, h)) for h in sample}

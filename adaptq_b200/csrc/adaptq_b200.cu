@@ -744,7 +744,9 @@ bool launch_sparse(Group *g, ComputeLaunch &a) {
 // ---- streaming kernel dispatch ---------------------------------------------
 template <int KB, int KW, int VB, int VW>
 bool launch_stream_t(Group *g, const StreamLaunch &a, int grid) {
-  auto kern = compute_stream_kernel<KB, KW, VB, VW>;
+  void (*kern)(const StreamLaunch);
+  if constexpr (KB == 3 || VB == 3) kern = compute_stream_kernel_fields<KB, KW, VB, VW>;
+  else kern = compute_stream_kernel<KB, KW, VB, VW>;
   static int configured[MAX_DEVICES] = {};
   if (!ensure_smem_limit(kern, configured, g->device, CS_SMEM_BYTES, "compute")) return false;
   launch_attention(g, kern, dim3((unsigned)grid), CS_THREADS, CS_SMEM_BYTES, a);

@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("kb,vb,kw,device", [
     ([16, 4, 4, 4], [2, 2, 2, 2], dict(v_mass=0.0, hybrid_thresh=0), True),
     ([16, 3, 3, 2, 2], [2, 2, 2, 4, 4], dict(v_mass=0.0, hybrid_thresh=0), False),   # three parts, host buffers
+    ([4, 4, 4, 3, 3, 4], [2, 2, 2, 2, 4, 4], dict(v_mass=0.0, hybrid_thresh=0), True), # four parts, all on the persistent kernel, own streams
     ([16, 4, 4], [2, 2, 2], dict(), True),                                           # Engine defaults
     (4, 4, dict(v_mass=0.0, hybrid_thresh=0), True),                                 # one part
 ])
